@@ -1,0 +1,172 @@
+/*
+ * moe_b200.h — C ABI of libmoe_b200.so: the MoE routing / dispatch hot path
+ * of santiweide/moe-routers rebuilt for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - every entry point returns an int status (MOE_OK == 0); nothing calls
+ *     exit(), nothing throws;
+ *   - all pointers are DEVICE pointers unless the name ends in _host;
+ *   - no entry point allocates or frees device memory and none synchronises
+ *     the host (the one exception says so); scratch comes from a caller-owned
+ *     workspace sized by moe_workspace_bytes();
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it;
+ *   - element type codes: MOE_F16, MOE_BF16, MOE_F32;
+ *   - the library keeps no mutable global state: calls on different streams
+ *     with different workspaces are independent.
+ *
+ * Each declaration names the piece of the reference (path:lines inside
+ * santiweide/moe-routers) that it replaces.
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MOE_OK = 0,
+  MOE_ERR_ARG = 1,        /* bad argument (null pointer, size, dtype, alignment) */
+  MOE_ERR_UNSUPPORTED = 2,/* shape outside what the kernels are built for */
+  MOE_ERR_WORKSPACE = 3,  /* workspace missing or too small */
+  MOE_ERR_LAUNCH = 4,     /* CUDA reported a launch / driver error */
+  MOE_ERR_DEVICE = 5      /* a kernel recorded an error in the status block */
+};
+
+enum { MOE_F16 = 0, MOE_BF16 = 1, MOE_F32 = 2 };
+
+/* Activation fused into the grouped GEMM epilogue. */
+enum { MOE_ACT_NONE = 0, MOE_ACT_GELU = 1, MOE_ACT_SILU = 2, MOE_ACT_SWIGLU = 3 };
+
+/* Storage of a weight matrix: MOE_W_KN = [K,N] row-major (N contiguous, what
+ * grouped_ffn_forward is given), MOE_W_NK = [N,K] row-major (nn.Linear). */
+enum { MOE_W_KN = 0, MOE_W_NK = 1 };
+
+/* Library version and a human-readable text for the last non-OK status
+ * returned on the calling thread. */
+int moe_version(void);
+const char* moe_last_error(void);
+
+/* Bytes of workspace the routing entry points need for `tokens` tokens,
+ * `experts` experts and `top_k` picks.  The first 256 bytes are the status
+ * block (see moe_read_status). */
+size_t moe_workspace_bytes(int tokens, int experts, int top_k);
+
+/* Zero the status block of a workspace (async on `stream`).  Call once after
+ * allocating the workspace. */
+int moe_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Copy the status block's first word to the host.  THIS CALL SYNCHRONISES
+ * `stream`.  0 means no kernel recorded an error; otherwise the value encodes
+ * which bounded wait gave up (see moe_last_error). */
+int moe_read_status(const void* workspace, void* stream, int* status_host);
+
+/*
+ * Top-k selection with softmax gates over the selected logits.
+ * Replaces: fused_select_cuda.forward(logits, k) as called by CUDATopKRouter
+ * (models/decoder_moe.py:137-151), torch.topk + softmax of TorchTopKRouter
+ * (models/decoder_moe.py:58-62) and top2_select_64_kernel
+ * (kernels/fused_select.cu:47-113).
+ *   logits [tokens, experts] row-major, dtype code `logits_dtype`
+ *   idx    [tokens, top_k] int32, descending logit order, lowest index wins ties
+ *   gates  [tokens, top_k] float32, softmax over the selected values
+ * Limits: 1 <= top_k <= 8, top_k <= experts <= 1024.
+ */
+int moe_topk_select(const void* logits, int logits_dtype, int tokens, int experts, int top_k,
+                    int32_t* idx, float* gates, void* stream);
+
+/*
+ * Count, scan and pack: expert-contiguous copy of the raw token rows.
+ * Replaces: count_expert_kernel, the CUB scan, the host read-back and
+ * pack_copy_kernel (kernels/fused_select.cu:116-198, :256-308) and the torch
+ * pack _pack_routes (bench_router.py:57-78).
+ *   x         [tokens, d] row-major, `elem_bytes` bytes per element (2 or 4)
+ *   idx       [tokens, top_k] int32 expert ids in [0, experts)
+ *   counts    [experts] int32            routes per expert
+ *   offsets   [experts + 1] int32        exclusive prefix, offsets[experts] = tokens*top_k
+ *   packed    [tokens*top_k, d]          row p holds x[row_route[p] / top_k], bit for bit
+ *   row_route [tokens*top_k] int32       route id (t*top_k + j) stored in packed row p
+ *   route_row [tokens*top_k] int32       inverse permutation (may be NULL)
+ * Order inside an expert segment is ascending route id (deterministic).
+ * `packed` may be NULL to compute only counts / offsets / maps.
+ */
+int moe_pack(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+             int top_k, int32_t* counts, int32_t* offsets, void* packed, int32_t* row_route,
+             int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Gate-weighted un-permute and sum over the top_k picks:
+ *   out[t] = sum_j gates[t,j] * y[route_row[t*top_k + j]]   (fp32 accumulate)
+ * Replaces: `expert(x_e) * w_e` + index_add_ (models/decoder_moe.py:270-271).
+ *   y [tokens*top_k, d] and out [tokens, d] have dtype `dtype` (MOE_F16 / MOE_BF16).
+ */
+int moe_combine(const void* y, int dtype, const float* gates, const int32_t* route_row, int tokens,
+                int d, int top_k, void* out, void* stream);
+
+/*
+ * Fused route: router logit GEMM (tcgen05 / TMEM, TMA-fed) whose epilogue adds
+ * the skew bias, selects top-k and computes the gates, followed by the pack.
+ * Replaces the whole `fused_select` strategy: x @ w.t() + skew
+ * (bench_router.py:512-516) and fused_select_forward
+ * (kernels/fused_select.cu:203-311); the logits never go to HBM unless
+ * `logits_out` is given.
+ *   x [tokens, d] fp16, w_router [experts, d] fp16 (both row-major, d % 8 == 0)
+ *   skew: logits[:, :skew_experts] += skew_bias, applied after the logits are
+ *         rounded to fp16 (the dtype the reference computes them in)
+ *   logits_out: NULL or [tokens, experts] float32 receiving the values the
+ *         selection saw
+ *   remaining outputs as in moe_topk_select and moe_pack.
+ * Limits: experts % 16 == 0, 16 <= experts <= 256, 1 <= top_k <= 8.
+ */
+int moe_route_fused(const void* x, const void* w_router, int tokens, int d, int experts, int top_k,
+                    int skew_experts, float skew_bias, int32_t* idx, float* gates, int32_t* counts,
+                    int32_t* offsets, void* packed, int32_t* row_route, int32_t* route_row,
+                    float* logits_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The logit GEMM + select half of moe_route_fused on its own (T_logit +
+ * T_select of bench_router.py:512-545 in one launch). */
+int moe_router_gemm_select(const void* x, const void* w_router, int tokens, int d, int experts,
+                           int top_k, int skew_experts, float skew_bias, int32_t* idx, float* gates,
+                           float* logits_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Sinkhorn-balanced routing.
+ * Replaces: SinkhornRouter.forward (models/decoder_moe.py:92-123) and the
+ * unbuilt kernels of kernels/fused_sinkhorn.cu:56-209.
+ *   q = exp(logits/temperature - rowmax); iters x { rows /= (sum+eps);
+ *   cols = cols/(sum+eps) * tokens/experts }; rows /= (sum+eps); top-k of q,
+ *   gates = vals / (sum(vals) + eps).
+ *   idx [tokens, top_k] int32, gates [tokens, top_k] float32.
+ * Limits: experts <= 64... see moe_last_error for the supported range.
+ */
+int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, int experts, int top_k, int iters,
+                 float epsilon, float temperature, int32_t* idx, float* gates, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/*
+ * Grouped expert GEMM over expert-contiguous rows (tcgen05 / TMEM, TMA-fed,
+ * persistent tile scheduler driven by the device-side offsets):
+ *   for every expert e: C[offsets[e]:offsets[e+1], :] =
+ *         act( A[offsets[e]:offsets[e+1], :] @ W[e] ) (* row_scale[row])
+ * Replaces: grouped_ffn_forward (kernels/grouped_ffn.cu:53-136) and the
+ * per-expert loops (bench_2gpu_pcie.py:123-171, models/decoder_moe.py:256-273,
+ * fused_select.py:74-93).
+ *   a [rows, K] fp16 row-major; w: `experts` matrices, stride_w elements apart,
+ *   each [K,N] (MOE_W_KN) or [N,K] (MOE_W_NK); c [rows, N] fp16
+ *   (for MOE_ACT_SWIGLU the weight has 2N output features, gate then up, and
+ *   c = silu(gate) * up has N columns)
+ *   offsets [experts+1] int32 on the device; `rows` is the capacity of a / c
+ *   row_scale: NULL or float32 [rows] multiplied into the result rows.
+ * Limits: K % 64 == 0, N % 64 == 0.
+ */
+int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts,
+                     int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
+                     const float* row_scale, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H_ */

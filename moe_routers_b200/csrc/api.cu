@@ -1,0 +1,70 @@
+// Library-level entry points: version, error text, workspace helpers.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace moe {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return MOE_OK;
+  return fail(MOE_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+}  // namespace moe
+
+extern "C" int moe_version(void) { return 100; }
+
+extern "C" const char* moe_last_error(void) { return moe::g_error; }
+
+extern "C" size_t moe_workspace_bytes(int tokens, int experts, int top_k) {
+  if (tokens < 0 || experts <= 0) return 0;
+  return moe::workspace_bytes_for(tokens, experts, top_k);
+}
+
+extern "C" int moe_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace moe;
+  if (!workspace || workspace_bytes < (size_t)(kStatusBytes + kControlBytes))
+    return fail(MOE_ERR_WORKSPACE, "moe_workspace_init: workspace too small");
+  const cudaError_t e = cudaMemsetAsync(workspace, 0, kStatusBytes + kControlBytes,
+                                        static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_workspace_init: %s", cudaGetErrorString(e));
+  return MOE_OK;
+}
+
+extern "C" int moe_read_status(const void* workspace, void* stream, int* status_host) {
+  using namespace moe;
+  if (!workspace || !status_host) return fail(MOE_ERR_ARG, "moe_read_status: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_read_status: %s", cudaGetErrorString(e));
+  *status_host = v;
+  if (v != 0) {
+    const char* what = (v & 0xf00) == kErrMbarTimeout   ? "an mbarrier wait gave up"
+                       : (v & 0xf00) == kErrGridBarrier ? "a grid barrier wait gave up"
+                       : (v & 0xf00) == kErrBadIndex    ? "an expert index was out of range"
+                                                        : "unknown device error";
+    return fail(MOE_ERR_DEVICE, "device status 0x%x: %s", v, what);
+  }
+  return MOE_OK;
+}

@@ -1,0 +1,118 @@
+// Top-k selection over router logits, one warp per token row.
+//
+// Replaces fused_select_cuda.forward(logits, k) (called at
+// models/decoder_moe.py:150), torch.topk + softmax (models/decoder_moe.py:58-62)
+// and top2_select_64_kernel (kernels/fused_select.cu:47-113).
+//
+// Each lane owns NPL consecutive columns (column = lane*NPL + i).  A pick is a
+// warp-wide arg-max under the ordering "larger value, then lower index"; the
+// winner is retired through a per-lane bit mask (not by overwriting the value,
+// so rows that contain -inf still select in index order).  Gates are the
+// softmax over the picked values, in fp32.
+#include "common.cuh"
+
+namespace moe {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+
+template <typename T, int NPL>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+topk_select_kernel(const T* __restrict__ logits, int32_t* __restrict__ out_idx,
+                   float* __restrict__ out_w, int tokens, int experts, int top_k) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= tokens) return;  // whole warp leaves together
+  const T* src = logits + (size_t)row * experts;
+
+  float v[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int col = lane * NPL + i;
+    v[i] = (col < experts) ? to_float(src[col]) : -INFINITY;
+  }
+  uint32_t taken = 0;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i)
+    if (lane * NPL + i >= experts) taken |= 1u << i;  // padding columns are never picked
+
+  float pick_v[8];
+  int pick_i[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j < top_k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int col = lane * NPL + i;
+        if (!((taken >> i) & 1u) && better(v[i], col, bv, bi)) { bv = v[i]; bi = col; }
+      }
+#pragma unroll
+      for (int ofs = 16; ofs > 0; ofs >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, ofs);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, ofs);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+      }
+      // every lane now holds the same winner
+      if (bi != 0x7fffffff && bi / NPL == lane) taken |= 1u << (bi % NPL);
+      pick_v[j] = bv;
+      pick_i[j] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+  }
+
+  if (lane == 0) {
+    const float m = pick_v[0];
+    float e[8];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < top_k) { e[j] = expf(pick_v[j] - m); sum += e[j]; }
+    const float inv = 1.f / fmaxf(sum, 1e-9f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < top_k) {
+        out_idx[(size_t)row * top_k + j] = pick_i[j];
+        out_w[(size_t)row * top_k + j] = e[j] * inv;
+      }
+  }
+}
+
+template <typename T>
+int launch_select(const void* logits, int tokens, int experts, int top_k, int32_t* idx, float* w,
+                  cudaStream_t s) {
+  const int grid = (tokens + kWarpsPerCta - 1) / kWarpsPerCta;
+  const T* p = static_cast<const T*>(logits);
+  const int npl = (experts + 31) / 32;
+#define MOE_SEL(N)                                                                         \
+  topk_select_kernel<T, N><<<grid, kWarpsPerCta * 32, 0, s>>>(p, idx, w, tokens, experts, top_k)
+  if (npl <= 1) MOE_SEL(1);
+  else if (npl <= 2) MOE_SEL(2);
+  else if (npl <= 4) MOE_SEL(4);
+  else if (npl <= 8) MOE_SEL(8);
+  else if (npl <= 16) MOE_SEL(16);
+  else MOE_SEL(32);
+#undef MOE_SEL
+  return check_launch("topk_select_kernel");
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_topk_select(const void* logits, int logits_dtype, int tokens, int experts,
+                               int top_k, int32_t* idx, float* gates, void* stream) {
+  using namespace moe;
+  if (tokens < 0 || experts <= 0) return fail(MOE_ERR_ARG, "moe_topk_select: bad shape [%d,%d]", tokens, experts);
+  if (top_k < 1 || top_k > 8) return fail(MOE_ERR_UNSUPPORTED, "moe_topk_select: top_k must be in [1,8], got %d", top_k);
+  if (top_k > experts) return fail(MOE_ERR_ARG, "moe_topk_select: top_k must be <= n_experts");
+  if (experts > 1024) return fail(MOE_ERR_UNSUPPORTED, "moe_topk_select: experts must be <= 1024, got %d", experts);
+  if (tokens == 0) return MOE_OK;
+  if (!logits || !idx || !gates) return fail(MOE_ERR_ARG, "moe_topk_select: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (logits_dtype) {
+    case MOE_F16: return launch_select<__half>(logits, tokens, experts, top_k, idx, gates, s);
+    case MOE_BF16: return launch_select<__nv_bfloat16>(logits, tokens, experts, top_k, idx, gates, s);
+    case MOE_F32: return launch_select<float>(logits, tokens, experts, top_k, idx, gates, s);
+    default: return fail(MOE_ERR_ARG, "moe_topk_select: logits must be fp16/bf16/fp32");
+  }
+}

@@ -1,0 +1,70 @@
+"""The C-ABI library loads and exports every symbol that include/moe_b200.h
+declares; argument validation works without a GPU (no kernel is launched)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from moe_routers_b200 import build
+
+    build.build_library()
+    from moe_routers_b200 import _lib
+
+    return _lib
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "moe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moe_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = _declared_functions()
+    assert len(names) >= 12
+    raw = ctypes.CDLL(lib.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in moe_b200.h but not exported"
+    assert sorted(lib.SIGNATURES) == names
+
+
+def test_version_and_workspace_size(lib):
+    assert lib.lib.moe_version() >= 100
+    small = lib.lib.moe_workspace_bytes(32, 64, 2)
+    big = lib.lib.moe_workspace_bytes(4096, 64, 2)
+    assert 512 < small <= big
+    assert lib.lib.moe_workspace_bytes(-1, 64, 2) == 0
+
+
+def test_argument_errors_do_not_launch(lib):
+    L = lib.lib
+    # top_k out of range -> MOE_ERR_UNSUPPORTED with a readable text
+    rc = L.moe_topk_select(None, lib.MOE_F16, 4, 64, 9, None, None, None)
+    assert rc == 2 and "top_k" in lib.last_error()
+    rc = L.moe_topk_select(None, 7, 4, 64, 2, None, None, None)
+    assert rc == 1
+    rc = L.moe_pack(None, 3, None, 4, 8, 64, 2, None, None, None, None, None, None, 0, None)
+    assert rc == 1 and "elem_bytes" in lib.last_error()
+    rc = L.moe_combine(None, lib.MOE_F32, None, None, 4, 8, 2, None, None)
+    assert rc == 1
+    with pytest.raises(lib.MoeError):
+        lib.check(rc)
+    # zero tokens is a valid no-op that needs no pointers
+    assert L.moe_topk_select(None, lib.MOE_F16, 0, 64, 2, None, None, None) == 0
+    assert L.moe_combine(None, lib.MOE_F16, None, None, 0, 8, 2, None, None) == 0
+
+
+def test_ops_reject_cpu_tensors(lib):
+    import torch
+    from moe_routers_b200 import ops
+
+    with pytest.raises(RuntimeError, match="inputs must be CUDA"):
+        ops.topk_select(torch.zeros(4, 64), 2)
+    with pytest.raises(RuntimeError, match="inputs must be CUDA"):
+        ops.pack(torch.zeros(4, 8, dtype=torch.float16), torch.zeros(4, 2, dtype=torch.int32), 64)
