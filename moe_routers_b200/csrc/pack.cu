@@ -7,20 +7,24 @@
 // Data flow (tile = 32 consecutive tokens = 32*k routes):
 //   pack_hist_kernel     idx -> tile_hist[tile][expert]           (skipped when the router GEMM
 //                                                                  epilogue already produced it)
-//   pack_scan_kernel     tile_hist -> tile_base (exclusive prefix down the tiles, per expert),
-//                        counts, offsets
-//   pack_scatter_kernel  per tile: ranks inside the tile by warp match/ballot, destination row =
-//                        offsets[e] + tile_base[tile][e] + rank, then 128-bit row copies
+//   pack_scan_kernel     (only above 256 tiles) tile_hist -> tile_base: exclusive prefix down the
+//                        tiles per expert, and counts
+//   pack_scatter_kernel  per tile: offsets (scan of the expert totals) and the tile's base per
+//                        expert, ranks inside the tile by warp match/ballot, destination row =
+//                        offsets[e] + routes to e in earlier tiles + rank, then 128-bit row copies
 // A destination row is a pure function of (idx, route id): the order inside an
 // expert segment is ascending route id, run to run.  There is no host
 // synchronisation: total rows = tokens * top_k is known in advance.
-#include "common.cuh"
+#include <cstdlib>
+
+#include "sm100.cuh"
 
 namespace moe {
 namespace {
 
 constexpr int kScatterThreads = 256;
 constexpr int kMaxTileRoutes = kTileTokens * 8;  // top_k <= 8
+constexpr int kFusedPrefixTiles = 256;           // up to this many tiles each scatter CTA sums the histograms itself
 
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -28,6 +32,7 @@ pack_hist_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ tile_his
                  int experts, int top_k, int32_t* status) {
   extern __shared__ int32_t s_hist[];
   const int tile = blockIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the scatter may prefetch its rows
   for (int e = threadIdx.x; e < experts; e += blockDim.x) s_hist[e] = 0;
   __syncthreads();
   const int r0 = tile * kTileTokens * top_k;
@@ -43,50 +48,39 @@ pack_hist_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ tile_his
 }
 
 // ---------------------------------------------------------------------------
-// One CTA.  Warp per expert column: exclusive prefix down the tiles; then an
-// exclusive scan over the expert totals gives offsets.
-__global__ void __launch_bounds__(1024)
+// Large inputs only (more than kFusedPrefixTiles tiles): one CTA per expert column computes the
+// exclusive prefix of that expert's tile counts down the tiles, and the expert's total.
+__global__ void __launch_bounds__(256)
 pack_scan_kernel(const int32_t* __restrict__ tile_hist, int32_t* __restrict__ tile_base,
-                 int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int num_tiles,
-                 int experts) {
-  extern __shared__ int32_t s_tot[];  // [experts] totals, then scanned in place
+                 int32_t* __restrict__ counts, int num_tiles, int experts) {
+  __shared__ int32_t s_warp[8];
+  const int e = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int nwarps = blockDim.x >> 5;
-  for (int e = warp; e < experts; e += nwarps) {
-    int running = 0;
-    for (int base = 0; base < num_tiles; base += 32) {
-      const int tile = base + lane;
-      const int h = (tile < num_tiles) ? tile_hist[(size_t)tile * experts + e] : 0;
-      int incl = h;
+  int running = 0;
+  for (int base = 0; base < num_tiles; base += 256) {
+    const int tile = base + threadIdx.x;
+    const int h = (tile < num_tiles) ? tile_hist[(size_t)tile * experts + e] : 0;
+    int incl = h;
 #pragma unroll
-      for (int ofs = 1; ofs < 32; ofs <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, incl, ofs);
-        if (lane >= ofs) incl += n;
-      }
-      if (tile < num_tiles) tile_base[(size_t)tile * experts + e] = running + incl - h;
-      running += __shfl_sync(0xffffffffu, incl, 31);
+    for (int ofs = 1; ofs < 32; ofs <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, ofs);
+      if (lane >= ofs) incl += n;
     }
-    if (lane == 0) { s_tot[e] = running; counts[e] = running; }
-  }
-  __syncthreads();
-  // exclusive scan over experts (experts <= 1024): serial per 32-chunk carry, warp 0
-  if (warp == 0) {
-    int carry = 0;
-    for (int base = 0; base < experts; base += 32) {
-      const int e = base + lane;
-      const int c = (e < experts) ? s_tot[e] : 0;
-      int incl = c;
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    int warp_ofs = 0, total = 0;
 #pragma unroll
-      for (int ofs = 1; ofs < 32; ofs <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, incl, ofs);
-        if (lane >= ofs) incl += n;
-      }
-      if (e < experts) offsets[e] = carry + incl - c;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
+    for (int w = 0; w < 8; ++w) {
+      const int v = s_warp[w];
+      if (w < warp) warp_ofs += v;
+      total += v;
     }
-    if (lane == 0) offsets[experts] = carry;
+    if (tile < num_tiles) tile_base[(size_t)tile * experts + e] = running + warp_ofs + incl - h;
+    running += total;
+    __syncthreads();
   }
+  if (threadIdx.x == 0) counts[e] = running;
 }
 
 // ---------------------------------------------------------------------------
@@ -112,32 +106,82 @@ __device__ __forceinline__ void copy_row(const char* __restrict__ src, char* con
   }
 }
 
-// grid = num_tiles * split; CTA (tile, part) ranks the whole tile (cheap) and
-// copies tokens [part*tokens_per_cta, ...) of it.
-template <typename V>
-__global__ void __launch_bounds__(kScatterThreads)
-pack_scatter_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
-                    const int32_t* __restrict__ tile_base, const int32_t* __restrict__ offsets,
-                    char* __restrict__ packed, int32_t* __restrict__ row_route,
-                    int32_t* __restrict__ route_row, int tokens, size_t row_bytes, int experts,
-                    int top_k, int split, int32_t* status) {
-  extern __shared__ int32_t s_mem[];
-  int32_t* s_base = s_mem;           // [experts]   next free row per expert inside this tile
-  int32_t* s_dst = s_mem + experts;  // [kMaxTileRoutes] destination row of each route (-1 = skip)
-
-  const int tile = blockIdx.x / split;
-  const int part = blockIdx.x % split;
+// Where a tile's rows start: offsets[e] (exclusive scan of the expert totals) plus the number of
+// routes to e in earlier tiles.  With tile_base == nullptr every CTA derives both from the tile
+// histograms itself (they are L2-resident and small); otherwise pack_scan_kernel has produced
+// tile_base and counts.  Then warp 0 ranks the routes of the tile with match/ballot.  On return
+// s_dst[r] holds the destination row of route r of the tile (-1 = skip) and the maps are written.
+// `publish` marks the one CTA of the grid that writes counts and offsets.
+__device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ idx,
+                                                  const int32_t* __restrict__ tile_hist,
+                                                  const int32_t* __restrict__ tile_base,
+                                                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                                                  int32_t* __restrict__ row_route,
+                                                  int32_t* __restrict__ route_row, int tile, int t0,
+                                                  int tile_routes, int experts, int top_k, int num_tiles,
+                                                  bool publish, bool write_maps, int32_t* s_base,
+                                                  int32_t* s_total, int32_t* s_dst, int32_t* status) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int t0 = tile * kTileTokens;
-  const int tile_tokens = min(kTileTokens, tokens - t0);
-  const int tile_routes = tile_tokens * top_k;
-
-  for (int e = threadIdx.x; e < experts; e += blockDim.x)
-    s_base[e] = offsets[e] + tile_base[(size_t)tile * experts + e];
+  if (tile_base != nullptr) {
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      s_base[e] = tile_base[(size_t)tile * experts + e];
+      s_total[e] = counts[e];
+    }
+  } else {
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) { s_base[e] = 0; s_total[e] = 0; }
+    __syncthreads();
+    const int parts = max(1, (int)blockDim.x / experts);
+    for (int cell = threadIdx.x; cell < experts * parts; cell += blockDim.x) {
+      const int e = cell % experts;
+      const int pt = cell / experts;
+      int before = 0, total = 0;
+      int t = pt;
+      for (; t + 7 * parts < num_tiles; t += 8 * parts) {
+        int h[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) h[u] = __ldg(tile_hist + (size_t)(t + u * parts) * experts + e);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          total += h[u];
+          if (t + u * parts < tile) before += h[u];
+        }
+      }
+      for (; t < num_tiles; t += parts) {
+        const int h = __ldg(tile_hist + (size_t)t * experts + e);
+        total += h;
+        if (t < tile) before += h;
+      }
+      atomicAdd(&s_base[e], before);
+      atomicAdd(&s_total[e], total);
+    }
+  }
   __syncthreads();
-
   if (warp == 0) {
+    // exclusive scan of the totals over experts; s_base becomes the first row of this tile per expert
+    int carry = 0;
+    for (int eb = 0; eb < experts; eb += 32) {
+      const int e = eb + lane;
+      const int c = (e < experts) ? s_total[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int ofs = 1; ofs < 32; ofs <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, ofs);
+        if (lane >= ofs) incl += n;
+      }
+      if (e < experts) {
+        const int excl = carry + incl - c;
+        s_base[e] += excl;
+        if (publish) {
+          offsets[e] = excl;
+          if (tile_base == nullptr) counts[e] = c;
+        }
+      }
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (publish && lane == 0) offsets[experts] = carry;
+    __syncwarp();
+
     for (int c = 0; c < tile_routes; c += 32) {
       const int r = c + lane;
       const bool in_tile = r < tile_routes;
@@ -157,7 +201,7 @@ pack_scatter_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
       if (in_tile) {
         const int dst = valid ? base + rank : -1;
         s_dst[r] = dst;
-        if (valid && part == 0) {
+        if (valid && write_maps) {
           const int route = t0 * top_k + r;
           row_route[dst] = route;
           if (route_row != nullptr) route_row[route] = dst;
@@ -167,6 +211,35 @@ pack_scatter_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
     }
   }
   __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// Load/store scatter for rows that are not 16-byte friendly.  grid = num_tiles * split; CTA
+// (tile, part) ranks the whole tile (cheap) and copies tokens [part*tokens_per_cta, ...) of it.
+template <typename V>
+__global__ void __launch_bounds__(kScatterThreads)
+pack_scatter_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
+                    const int32_t* __restrict__ tile_hist, const int32_t* __restrict__ tile_base,
+                    int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                    char* __restrict__ packed, int32_t* __restrict__ row_route,
+                    int32_t* __restrict__ route_row, int tokens, size_t row_bytes, int experts,
+                    int top_k, int split, int num_tiles, int32_t* status) {
+  extern __shared__ int32_t s_mem[];
+  int32_t* s_base = s_mem;               // [experts]
+  int32_t* s_total = s_mem + experts;    // [experts]
+  int32_t* s_dst = s_mem + 2 * experts;  // [kMaxTileRoutes]
+
+  const int tile = blockIdx.x / split;
+  const int part = blockIdx.x % split;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int t0 = tile * kTileTokens;
+  const int tile_tokens = min(kTileTokens, tokens - t0);
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  tile_destinations(idx, tile_hist, tile_base, counts, offsets, row_route, route_row, tile, t0,
+                    tile_tokens * top_k, experts, top_k, num_tiles, blockIdx.x == 0, part == 0, s_base,
+                    s_total, s_dst, status);
   if (packed == nullptr) return;
 
   const int per_cta = kTileTokens / split;
@@ -184,6 +257,130 @@ pack_scatter_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Bulk-copy scatter (rows a multiple of 16 bytes, 16-byte aligned bases): one CTA per tile of 32
+// tokens.  Token rows are staged through a ring of shared-memory buffers by the TMA engine:
+//   global --cp.async.bulk--> shared (mbarrier complete_tx) --cp.async.bulk--> top_k global rows.
+// A row longer than kChunkBytes is moved in chunks.  Lane 0 of each of the 8 warps drives every
+// 8th item (item = row chunk); buffer (item % NBUF) with NBUF a multiple of 8, so a buffer is only
+// ever reused by the thread that filled it, after that thread's stores have finished reading it.
+// The first loads are issued before the destinations are known: they do not depend on the routing.
+constexpr int kChunkBytes = 8192;
+constexpr int kBulkIssuers = kScatterThreads / 32;
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+__global__ void __launch_bounds__(kScatterThreads, 1)
+pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
+                         const int32_t* __restrict__ tile_hist, const int32_t* __restrict__ tile_base,
+                         int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                         char* __restrict__ packed, int32_t* __restrict__ row_route,
+                         int32_t* __restrict__ route_row, int tokens, size_t row_bytes, int experts,
+                         int top_k, int num_tiles, int nbuf, int chunk_bytes, int32_t* status) {
+  extern __shared__ __align__(128) uint8_t s_raw[];
+  uint8_t* s_buf = s_raw;                                                        // [nbuf][chunk_bytes]
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_buf + (size_t)nbuf * chunk_bytes);  // [nbuf]
+  int32_t* s_base = reinterpret_cast<int32_t*>(s_bar + nbuf);                    // [experts]
+  int32_t* s_total = s_base + experts;                                           // [experts]
+  int32_t* s_dst = s_total + experts;                                            // [kMaxTileRoutes]
+
+  const int tile = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int t0 = tile * kTileTokens;
+  const int tile_tokens = min(kTileTokens, tokens - t0);
+  const int chunks = (int)((row_bytes + chunk_bytes - 1) / chunk_bytes);
+  const int items = packed != nullptr ? tile_tokens * chunks : 0;
+  const int depth = nbuf / kBulkIssuers;  // buffers owned by each issuing thread
+
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < nbuf; ++b)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(s_bar + b)) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const uint32_t buf0 = (uint32_t)__cvta_generic_to_shared(s_buf);
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(s_bar);
+  // item m of this thread is tile item (warp + m*8); it lives in buffer (warp + (m % depth)*8)
+  auto item_src = [&](int it, uint32_t& bytes) -> const char* {
+    const int row = it / chunks, ch = it % chunks;
+    const size_t ofs = (size_t)ch * chunk_bytes;
+    bytes = (uint32_t)min((size_t)chunk_bytes, row_bytes - ofs);
+    return x + (size_t)(t0 + row) * row_bytes + ofs;
+  };
+  if (lane == 0) {
+    for (int m = 0; m < depth; ++m) {
+      const int it = warp + m * kBulkIssuers;
+      if (it >= items) break;
+      uint32_t bytes;
+      const char* src = item_src(it, bytes);
+      const int b = warp + m * kBulkIssuers;
+      bulk_load(buf0 + (uint32_t)b * chunk_bytes, src, bytes, bar0 + 8u * b);
+    }
+  }
+  __syncwarp();
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  tile_destinations(idx, tile_hist, tile_base, counts, offsets, row_route, route_row, tile, t0,
+                    tile_tokens * top_k, experts, top_k, num_tiles, blockIdx.x == 0, true, s_base, s_total,
+                    s_dst, status);
+
+  if (lane == 0) {
+    bool ok = true;
+    for (int m = 0; ok; ++m) {
+      const int it = warp + m * kBulkIssuers;
+      if (it >= items) break;
+      const int b = warp + (m % depth) * kBulkIssuers;
+      ok = sm100::mbar_wait(bar0 + 8u * b, (uint32_t)(m / depth) & 1u, status, 8);
+      if (!ok) break;
+      const int row = it / chunks, ch = it % chunks;
+      uint32_t bytes;
+      (void)item_src(it, bytes);
+      for (int j = 0; j < top_k; ++j) {
+        const int d = s_dst[row * top_k + j];
+        if (d >= 0)
+          bulk_store(packed + (size_t)d * row_bytes + (size_t)ch * chunk_bytes, buf0 + (uint32_t)b * chunk_bytes, bytes);
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      const int nxt = it + depth * kBulkIssuers;
+      if (nxt < items) {
+        // the buffer is refilled once the stores just issued have finished reading it
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        uint32_t nbytes;
+        const char* src = item_src(nxt, nbytes);
+        bulk_load(buf0 + (uint32_t)b * chunk_bytes, src, nbytes, bar0 + 8u * b);
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores complete before the CTA retires
+  }
+  __syncwarp();
+}
+
+__global__ void pack_zero_kernel(int32_t* counts, int32_t* offsets, int experts) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < experts) counts[e] = 0;
+  if (e <= experts) offsets[e] = 0;
+}
+
+// MOE_B200_PDL=0 in the environment turns programmatic dependent launch off (plain stream order).
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("MOE_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 int pick_split(int num_tiles) {
   // aim for a few CTAs per SM (148 SMs) without dropping below one token per warp
   int split = 1;
@@ -193,34 +390,78 @@ int pick_split(int num_tiles) {
 
 }  // namespace
 
-// Shared by moe_pack and moe_route_fused: scan + scatter from ready tile histograms.
+// Shared by moe_pack and moe_route_fused: offsets + scatter from ready tile histograms.
 int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d,
                         int experts, int top_k, int32_t* counts, int32_t* offsets, void* packed,
                         int32_t* row_route, int32_t* route_row, const Workspace& ws,
                         cudaStream_t s) {
-  pack_scan_kernel<<<1, 1024, experts * sizeof(int32_t), s>>>(ws.tile_hist, ws.tile_base, counts,
-                                                             offsets, tokens > 0 ? ws.num_tiles : 0,
-                                                             experts);
-  int rc = check_launch("pack_scan_kernel");
-  if (rc != MOE_OK || tokens == 0) return rc;
-
+  if (tokens == 0) {
+    pack_zero_kernel<<<(experts + 256) / 256, 256, 0, s>>>(counts, offsets, experts);
+    return check_launch("pack_zero_kernel");
+  }
+  const int32_t* tile_base = nullptr;
+  if (ws.num_tiles > kFusedPrefixTiles) {
+    pack_scan_kernel<<<experts, 256, 0, s>>>(ws.tile_hist, ws.tile_base, counts, ws.num_tiles, experts);
+    const int rc = check_launch("pack_scan_kernel");
+    if (rc != MOE_OK) return rc;
+    tile_base = ws.tile_base;
+  }
   const size_t row_bytes = (size_t)d * elem_bytes;
-  const int split = pick_split(ws.num_tiles);
-  const int grid = ws.num_tiles * split;
-  const size_t smem = (size_t)(experts + kMaxTileRoutes) * sizeof(int32_t);
   const uintptr_t align = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) | row_bytes;
   const char* xs = static_cast<const char*>(x);
   char* ps = static_cast<char*>(packed);
-#define MOE_SCATTER(V)                                                                          \
-  pack_scatter_kernel<V><<<grid, kScatterThreads, smem, s>>>(xs, idx, ws.tile_base, offsets, ps, \
-                                                             row_route, route_row, tokens,      \
-                                                             row_bytes, experts, top_k, split,  \
-                                                             ws.status)
+  const int32_t* th = ws.tile_hist;
+  int32_t* st = ws.status;
+  const int nt = ws.num_tiles;
+
+  // Programmatic dependent launch: the scatter may become resident while the producer of the tile
+  // histograms (router GEMM or histogram kernel) is still running; it prefetches token rows and
+  // then blocks in griddepcontrol.wait until that kernel has completed.
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kScatterThreads, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (tile_base == nullptr && pdl_enabled()) ? 1 : 0;
+  cudaError_t err;
+
+  if ((align & 15) == 0 && packed != nullptr) {
+    const int chunk = (int)(row_bytes < (size_t)kChunkBytes ? row_bytes : (size_t)kChunkBytes);
+    const int chunks = (int)((row_bytes + chunk - 1) / chunk);
+    const size_t fixed = (size_t)(2 * experts + kMaxTileRoutes) * sizeof(int32_t) + 64 * sizeof(uint64_t) + 128;
+    int nbuf = (int)((227 * 1024 - fixed) / chunk);
+    const int want = ((kTileTokens * chunks + kBulkIssuers - 1) / kBulkIssuers) * kBulkIssuers;
+    if (nbuf > want) nbuf = want;
+    if (nbuf > 64) nbuf = 64;
+    nbuf = (nbuf / kBulkIssuers) * kBulkIssuers;
+    if (nbuf >= kBulkIssuers) {
+      const size_t smem = (size_t)nbuf * chunk + (size_t)nbuf * sizeof(uint64_t) +
+                         (size_t)(2 * experts + kMaxTileRoutes) * sizeof(int32_t);
+      err = cudaFuncSetAttribute(pack_scatter_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_bulk_kernel: %s", cudaGetErrorString(err));
+      cfg.gridDim = dim3(nt, 1, 1);
+      cfg.dynamicSmemBytes = smem;
+      err = cudaLaunchKernelEx(&cfg, pack_scatter_bulk_kernel, xs, idx, th, tile_base, counts, offsets, ps,
+                               row_route, route_row, tokens, row_bytes, experts, top_k, nt, nbuf, chunk, st);
+      if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_bulk_kernel: %s", cudaGetErrorString(err));
+      return MOE_OK;
+    }
+  }
+
+  const int split = pick_split(nt);
+  cfg.gridDim = dim3(nt * split, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)(2 * experts + kMaxTileRoutes) * sizeof(int32_t);
+#define MOE_SCATTER(V)                                                                            \
+  err = cudaLaunchKernelEx(&cfg, pack_scatter_kernel<V>, xs, idx, th, tile_base, counts, offsets, ps, \
+                           row_route, route_row, tokens, row_bytes, experts, top_k, split, nt, st)
   if ((align & 15) == 0) MOE_SCATTER(uint4);
   else if ((align & 3) == 0) MOE_SCATTER(uint32_t);
   else MOE_SCATTER(uint16_t);
 #undef MOE_SCATTER
-  return check_launch("pack_scatter_kernel");
+  if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_kernel: %s", cudaGetErrorString(err));
+  return MOE_OK;
 }
 
 }  // namespace moe

@@ -1,14 +1,6 @@
 // Entry points whose kernels are not linked yet answer MOE_ERR_UNSUPPORTED.
 #include "common.cuh"
 using namespace moe;
-extern "C" int moe_route_fused(const void*, const void*, int, int, int, int, int, float, int32_t*, float*, int32_t*,
-                               int32_t*, void*, int32_t*, int32_t*, float*, void*, size_t, void*) {
-  return fail(MOE_ERR_UNSUPPORTED, "moe_route_fused: not built");
-}
-extern "C" int moe_router_gemm_select(const void*, const void*, int, int, int, int, int, float, int32_t*, float*,
-                                      float*, void*, size_t, void*) {
-  return fail(MOE_ERR_UNSUPPORTED, "moe_router_gemm_select: not built");
-}
 extern "C" int moe_sinkhorn(const void*, int, int, int, int, int, float, float, int32_t*, float*, void*, size_t, void*) {
   return fail(MOE_ERR_UNSUPPORTED, "moe_sinkhorn: not built");
 }
