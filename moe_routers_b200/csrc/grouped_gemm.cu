@@ -1,0 +1,331 @@
+// Grouped expert GEMM over expert-contiguous rows (tcgen05 / TMEM / TMA).
+//
+// Replaces grouped_ffn_forward (kernels/grouped_ffn.cu:53-136, a CUTLASS mma.sync grouped GEMM fed
+// by host-built pointer arrays) and the per-expert Python loops around cuBLAS
+// (bench_2gpu_pcie.py:123-171, models/decoder_moe.py:256-273, fused_select.py:74-93).
+//
+//   for every expert e:  C[off[e]:off[e+1], :] = act( A[off[e]:off[e+1], :] @ W[e] ) (* row_scale)
+//
+// A persistent grid (one CTA per SM) walks the tile list (expert, n-tile, m-tile); the list is
+// derived on the device from the pack offsets, so there is no host synchronisation and no
+// per-call pointer table.  Tiles of one expert that share a weight n-tile are adjacent in the
+// list, so CTAs that run at the same time read the same weight tile through L2.
+//
+// Tile 128 x BN x 64, UMMA 128 x BN x 16 (fp16 in, fp32 accumulate in TMEM).  Two TMEM accumulators:
+// the epilogue of tile i (TMEM -> registers -> activation -> fp16 -> global, rows past the end of
+// the expert's segment masked) overlaps the main loop of tile i+1.
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4)..).
+#include "sm100.cuh"
+
+namespace moe {
+namespace {
+
+using namespace sm100;
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kUK = 16;
+constexpr int kThreads = 192;
+constexpr int kABytes = kBM * kBK * 2;
+constexpr int kMaxStages = 8;
+constexpr int kMaxExperts = 1024;
+
+struct GParams {
+  const int32_t* offsets;
+  int experts, rows, K, n_out, bn, n_tiles, kblocks, stages;
+  int w_kn;     // 1: weights stored [K, N] (N contiguous) -> MN-major B operand
+  int act;      // MOE_ACT_*
+  const float* row_scale;
+  __half* c;
+  int32_t* status;
+};
+
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
+__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+
+// tile id -> (expert, n tile, m tile).  s_mt[e] = number of 128-row tiles of experts < e.
+__device__ __forceinline__ void decode_tile(const int32_t* s_mt, int experts, int n_tiles, int t, int& e, int& nt,
+                                            int& mt) {
+  int lo = 0, hi = experts;  // largest e with s_mt[e] * n_tiles <= t
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if ((long long)s_mt[mid] * n_tiles <= t) lo = mid; else hi = mid;
+  }
+  e = lo;
+  const int mte = s_mt[e + 1] - s_mt[e];
+  const int local = t - s_mt[e] * n_tiles;
+  nt = local / mte;
+  mt = local % mte;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                    const GParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    record_error(p.status, kErrBadIndex | 0xfe);
+    return;
+  }
+  const int BN = p.bn;                    // accumulator columns per tile (256 / 128 / 64)
+  const int b_bytes = BN * kBK * 2;
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + (size_t)p.stages * kABytes;
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(sB + (size_t)p.stages * b_bytes);
+  // full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2]
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);
+  int32_t* s_mt = reinterpret_cast<int32_t*>(s_tmem + 4);  // [experts + 1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(s_bar);
+  const uint32_t empty0 = smem_u32(s_bar + kMaxStages);
+  const uint32_t tfull0 = smem_u32(s_bar + 2 * kMaxStages);
+  const uint32_t tempty0 = smem_u32(s_bar + 2 * kMaxStages + 2);
+  const uint32_t tmem_cols = (uint32_t)(2 * BN < 32 ? 32 : 2 * BN);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull0 + 8 * b, 1);
+      mbar_init(tempty0 + 8 * b, 128);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(s_tmem), tmem_cols);
+    tmem_relinquish();
+  }
+  // number of m tiles before each expert (serial prefix by one warp; experts <= 1024)
+  if (warp == 2) {
+    int carry = 0;
+    for (int eb = 0; eb < p.experts; eb += 32) {
+      const int e = eb + lane;
+      int cnt = 0;
+      if (e < p.experts) {
+        const int lo = p.offsets[e], hi = p.offsets[e + 1];
+        cnt = hi > lo ? (hi - lo + kBM - 1) / kBM : 0;
+      }
+      int incl = cnt;
+#pragma unroll
+      for (int ofs = 1; ofs < 32; ofs <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, ofs);
+        if (lane >= ofs) incl += n;
+      }
+      if (e < p.experts) s_mt[e] = carry + incl - cnt;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_mt[p.experts] = carry;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  const int total_tiles = s_mt[p.experts] * p.n_tiles;
+  const bool swiglu = p.act == MOE_ACT_SWIGLU;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;  // k-block counter across tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int e, nt, mt;
+        decode_tile(s_mt, p.experts, p.n_tiles, t, e, nt, mt);
+        const int row0 = p.offsets[e] + mt * kBM;
+        const int half = BN / 2;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = (int)(it % (uint32_t)p.stages);
+          const uint32_t ph = (it / (uint32_t)p.stages) & 1u;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1)) { ok = false; break; }
+          mbar_expect_tx(full0 + 8 * s, (uint32_t)(kABytes + b_bytes));
+          tma_load_2d(smem_u32(sA + (size_t)s * kABytes), &tmap_a, full0 + 8 * s, kb * kBK, row0);
+          const uint32_t sb = smem_u32(sB + (size_t)s * b_bytes);
+          if (!p.w_kn) {
+            // weights [E, Nw, K]: K-major B, one box of BN rows (SwiGLU: gate rows and up rows)
+            if (!swiglu) {
+              tma_load_3d(sb, &tmap_w, full0 + 8 * s, kb * kBK, nt * BN, e);
+            } else {
+              tma_load_3d(sb, &tmap_w, full0 + 8 * s, kb * kBK, nt * half, e);
+              tma_load_3d(sb + (uint32_t)half * kBK * 2, &tmap_w, full0 + 8 * s, kb * kBK, p.n_out + nt * half, e);
+            }
+          } else {
+            // weights [E, K, Nw]: MN-major B, boxes of 64 (N) x 64 (K), one per 64 output columns
+            for (int j = 0; j < BN / 64; ++j) {
+              int ncol = nt * BN + j * 64;
+              if (swiglu) ncol = (j < BN / 128) ? nt * half + j * 64 : p.n_out + nt * half + (j - BN / 128) * 64;
+              tma_load_3d(sb + (uint32_t)j * 8192u, &tmap_w, full0 + 8 * s, ncol, kb * kBK, e);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(kBM, BN, 0, 0, p.w_kn);
+      uint32_t it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const int ab = local & 1;
+        if (!mbar_wait(tempty0 + 8 * ab, (((uint32_t)local >> 1) & 1u) ^ 1u, p.status, 4)) break;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = (int)(it % (uint32_t)p.stages);
+          const uint32_t ph = (it / (uint32_t)p.stages) & 1u;
+          if (!mbar_wait(full0 + 8 * s, ph, p.status, 2)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + (size_t)s * kABytes);
+          const uint32_t b_addr = smem_u32(sB + (size_t)s * b_bytes);
+          const uint64_t adesc = make_desc_kmajor_sw128(a_addr);
+#pragma unroll
+          for (int k = 0; k < kBK / kUK; ++k) {
+            uint64_t bdesc;
+            if (!p.w_kn) bdesc = make_desc_kmajor_sw128(b_addr) + 2 * k;          // +32 B along K
+            else bdesc = make_desc_mnmajor_sw128(b_addr + (uint32_t)k * 2048u, 8192u);  // +16 K rows of 128 B
+            umma_f16(acc, adesc + 2 * k, bdesc, idesc, (uint32_t)((kb | k) != 0));
+          }
+          umma_commit(empty0 + 8 * s);
+        }
+        umma_commit(tfull0 + 8 * ab);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue -----------------------------------
+    const int q = warp & 3;
+    int local = 0;
+    const int out_bn = swiglu ? BN / 2 : BN;  // output columns per tile
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      int e, nt, mt;
+      decode_tile(s_mt, p.experts, p.n_tiles, t, e, nt, mt);
+      const int ab = local & 1;
+      const int seg_end = min(p.offsets[e + 1], p.rows);
+      const int grow = p.offsets[e] + mt * kBM + q * 32 + lane;
+      const bool valid = grow < seg_end && grow >= 0;
+      if (!mbar_wait(tfull0 + 8 * ab, ((uint32_t)local >> 1) & 1u, p.status, 3)) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
+      const float scale = (valid && p.row_scale != nullptr) ? p.row_scale[grow] : 1.f;
+      __half* crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
+      for (int c0 = 0; c0 < out_bn; c0 += 32) {
+        float v[32];
+        tmem_ld32(acc + (uint32_t)c0, v);
+        if (swiglu) {
+          float u[32];
+          tmem_ld32(acc + (uint32_t)(out_bn + c0), u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
+        } else if (p.act == MOE_ACT_GELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+        } else if (p.act == MOE_ACT_SILU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
+        }
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(crow + c0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __half2 h0 = __floats2half2_rn(v[8 * i + 0] * scale, v[8 * i + 1] * scale);
+            __half2 h1 = __floats2half2_rn(v[8 * i + 2] * scale, v[8 * i + 3] * scale);
+            __half2 h2 = __floats2half2_rn(v[8 * i + 4] * scale, v[8 * i + 5] * scale);
+            __half2 h3 = __floats2half2_rn(v[8 * i + 6] * scale, v[8 * i + 7] * scale);
+            uint4 o;
+            o.x = *reinterpret_cast<uint32_t*>(&h0);
+            o.y = *reinterpret_cast<uint32_t*>(&h1);
+            o.z = *reinterpret_cast<uint32_t*>(&h2);
+            o.w = *reinterpret_cast<uint32_t*>(&h3);
+            dst[i] = o;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty0 + 8 * ab);  // this thread is done reading the accumulator
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts, int rows,
+                                int K, int N, int w_layout, int64_t stride_w, int activation,
+                                const float* row_scale, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace moe;
+  if (experts <= 0 || rows < 0 || K <= 0 || N <= 0) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad shape");
+  if (experts > kMaxExperts) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: experts must be <= %d", kMaxExperts);
+  if (K % 8 != 0) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: K must be a multiple of 8, got %d", K);
+  if (N % 64 != 0) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: N must be a multiple of 64, got %d", N);
+  if (activation < MOE_ACT_NONE || activation > MOE_ACT_SWIGLU) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad activation");
+  if (w_layout != MOE_W_KN && w_layout != MOE_W_NK) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad weight layout");
+  if (rows == 0) return MOE_OK;
+  if (!a || !w || !c || !offsets) return fail(MOE_ERR_ARG, "moe_grouped_gemm: null pointer");
+  if (!workspace || workspace_bytes < (size_t)kStatusBytes) return fail(MOE_ERR_WORKSPACE, "moe_grouped_gemm: workspace missing");
+  const bool swiglu = activation == MOE_ACT_SWIGLU;
+  const int n_w = swiglu ? 2 * N : N;  // output features held by one weight matrix
+
+  GParams p;
+  p.offsets = offsets; p.experts = experts; p.rows = rows; p.K = K; p.n_out = N;
+  // accumulator columns per tile; SwiGLU tiles hold `bn/2` gate and `bn/2` up columns
+  int out_bn = N % 256 == 0 ? 256 : (N % 128 == 0 ? 128 : 64);
+  if (swiglu && out_bn > 128) out_bn = 128;
+  p.bn = swiglu ? 2 * out_bn : out_bn;
+  p.n_tiles = N / out_bn;
+  p.kblocks = (K + kBK - 1) / kBK;
+  p.w_kn = w_layout == MOE_W_KN;
+  p.act = activation;
+  p.row_scale = row_scale;
+  p.c = static_cast<__half*>(c);
+  p.status = static_cast<int32_t*>(workspace);
+
+  CUtensorMap tmap_a, tmap_w;
+  int rc = encode_tmap_2d(&tmap_a, a, (uint64_t)rows, (uint64_t)K, (uint64_t)K * 2, kBK, kBM);
+  if (rc != MOE_OK) return rc;
+  if (!p.w_kn) {
+    const uint32_t box_rows = swiglu ? (uint32_t)out_bn : (uint32_t)p.bn;
+    rc = encode_tmap_3d(&tmap_w, w, (uint64_t)experts, (uint64_t)n_w, (uint64_t)K, (uint64_t)K * 2,
+                        (uint64_t)stride_w * 2, kBK, box_rows);
+  } else {
+    rc = encode_tmap_3d(&tmap_w, w, (uint64_t)experts, (uint64_t)K, (uint64_t)n_w, (uint64_t)n_w * 2,
+                        (uint64_t)stride_w * 2, 64, kBK);
+  }
+  if (rc != MOE_OK) return rc;
+
+  const int stage_bytes = kABytes + p.bn * kBK * 2;
+  const int fixed = (2 * kMaxStages + 4) * 8 + 16 + (experts + 1) * 4 + 64;
+  int stages = (227 * 1024 - fixed) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: shared memory budget exceeded");
+  p.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes + fixed;
+
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  // upper bound of the tile count known on the host: every expert may add one partial m tile
+  const long long max_tiles = ((long long)rows / kBM + experts) * p.n_tiles;
+  const int grid = (int)(max_tiles < sms ? max_tiles : sms);
+
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_grouped_gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  grouped_gemm_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tmap_a, tmap_w, p);
+  return check_launch("grouped_gemm_kernel");
+}

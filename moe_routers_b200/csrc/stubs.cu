@@ -4,7 +4,3 @@ using namespace moe;
 extern "C" int moe_sinkhorn(const void*, int, int, int, int, int, float, float, int32_t*, float*, void*, size_t, void*) {
   return fail(MOE_ERR_UNSUPPORTED, "moe_sinkhorn: not built");
 }
-extern "C" int moe_grouped_gemm(const void*, const void*, void*, const int32_t*, int, int, int, int, int, int64_t, int,
-                                const float*, void*, size_t, void*) {
-  return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: not built");
-}
