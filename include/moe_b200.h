@@ -140,7 +140,10 @@ int moe_router_gemm_select(const void* x, const void* w_router, int tokens, int 
  *   cols = cols/(sum+eps) * tokens/experts }; rows /= (sum+eps); top-k of q,
  *   gates = vals / (sum(vals) + eps).
  *   idx [tokens, top_k] int32, gates [tokens, top_k] float32.
- * Limits: experts <= 64... see moe_last_error for the supported range.
+ * Limits: top_k <= 8, experts <= 1024, tokens * experts * 4 bytes / (number of SMs) must fit in
+ * shared memory (about 7 M matrix entries on a B200).  The kernel runs as a cooperative grid
+ * with one grid barrier per iteration; if a barrier wait gives up, the status block records it
+ * and the workspace must be re-initialised with moe_workspace_init.
  */
 int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, int experts, int top_k, int iters,
                  float epsilon, float temperature, int32_t* idx, float* gates, void* workspace,
@@ -160,7 +163,8 @@ int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, int experts, 
  *   c = silu(gate) * up has N columns)
  *   offsets [experts+1] int32 on the device; `rows` is the capacity of a / c
  *   row_scale: NULL or float32 [rows] multiplied into the result rows.
- * Limits: K % 64 == 0, N % 64 == 0.
+ * Limits: K % 8 == 0; N % 16 == 0 for [N,K] weights, N % 64 == 0 for [K,N] weights;
+ * experts <= 1024.
  */
 int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts,
                      int rows, int K, int N, int w_layout, int64_t stride_w, int activation,

@@ -17,10 +17,11 @@ namespace moe {
 // [256, 512)          control block: tickets / barrier counters (self-resetting)
 // [512, ...)          tile histograms  int32 [num_tiles][experts]
 //                     tile bases       int32 [num_tiles][experts]
-//                     split-K partials of the router GEMM (if used)
+//                     float scratch    float [2][kMaxGridBlocks][experts]  (Sinkhorn column partials)
 constexpr int kStatusBytes = 256;
 constexpr int kControlBytes = 256;
 constexpr int kTileTokens = 32;  // tokens per histogram tile (router GEMM epilogue and pack agree)
+constexpr int kMaxGridBlocks = 256;  // upper bound of the co-resident grid of the Sinkhorn kernel
 
 // Device-side error codes written to status word 0 (first error wins).
 constexpr int kErrMbarTimeout = 0x100;   // | role id
@@ -32,6 +33,7 @@ struct Workspace {
   int32_t* control;
   int32_t* tile_hist;
   int32_t* tile_base;
+  float* fscratch;
   int num_tiles;
 };
 
@@ -41,7 +43,7 @@ inline size_t workspace_bytes_for(int tokens, int experts, int /*top_k*/) {
   size_t tiles = (size_t)num_tiles_for(tokens > 0 ? tokens : 1);
   size_t hist = tiles * (size_t)experts * sizeof(int32_t);
   hist = (hist + 255) & ~(size_t)255;
-  return (size_t)kStatusBytes + kControlBytes + 2 * hist;
+  return (size_t)kStatusBytes + kControlBytes + 2 * hist + 2 * (size_t)kMaxGridBlocks * experts * sizeof(float);
 }
 
 inline Workspace carve(void* ws, int tokens, int experts) {
@@ -54,6 +56,7 @@ inline Workspace carve(void* ws, int tokens, int experts) {
   hist = (hist + 255) & ~(size_t)255;
   w.tile_hist = reinterpret_cast<int32_t*>(p + kStatusBytes + kControlBytes);
   w.tile_base = reinterpret_cast<int32_t*>(p + kStatusBytes + kControlBytes + hist);
+  w.fscratch = reinterpret_cast<float*>(p + kStatusBytes + kControlBytes + 2 * hist);
   return w;
 }
 

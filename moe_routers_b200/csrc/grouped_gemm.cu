@@ -59,6 +59,47 @@ __device__ __forceinline__ void decode_tile(const int32_t* s_mt, int experts, in
   mt = local % mte;
 }
 
+template <int W>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[W]) {
+  if constexpr (W == 32) tmem_ld32(taddr, v); else tmem_ld16(taddr, v);
+}
+
+// W accumulator columns of one row: TMEM -> registers -> activation -> fp16 -> global.
+template <int W>
+__device__ __forceinline__ void epilogue_chunk(uint32_t t_main, uint32_t t_up, bool swiglu, int act, float scale,
+                                               bool valid, __half* dst_h) {
+  float v[W];
+  tmem_ld<W>(t_main, v);
+  if (swiglu) {
+    float u[W];
+    tmem_ld<W>(t_up, u);
+#pragma unroll
+    for (int i = 0; i < W; ++i) v[i] = silu(v[i]) * u[i];
+  } else if (act == MOE_ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) v[i] = gelu_erf(v[i]);
+  } else if (act == MOE_ACT_SILU) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) v[i] = silu(v[i]);
+  }
+  if (valid) {
+    uint4* dst = reinterpret_cast<uint4*>(dst_h);
+#pragma unroll
+    for (int i = 0; i < W / 8; ++i) {
+      __half2 h0 = __floats2half2_rn(v[8 * i + 0] * scale, v[8 * i + 1] * scale);
+      __half2 h1 = __floats2half2_rn(v[8 * i + 2] * scale, v[8 * i + 3] * scale);
+      __half2 h2 = __floats2half2_rn(v[8 * i + 4] * scale, v[8 * i + 5] * scale);
+      __half2 h3 = __floats2half2_rn(v[8 * i + 6] * scale, v[8 * i + 7] * scale);
+      uint4 o;
+      o.x = *reinterpret_cast<uint32_t*>(&h0);
+      o.y = *reinterpret_cast<uint32_t*>(&h1);
+      o.z = *reinterpret_cast<uint32_t*>(&h2);
+      o.w = *reinterpret_cast<uint32_t*>(&h3);
+      dst[i] = o;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const GParams p) {
@@ -217,37 +258,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
       const float scale = (valid && p.row_scale != nullptr) ? p.row_scale[grow] : 1.f;
       __half* crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
-      for (int c0 = 0; c0 < out_bn; c0 += 32) {
-        float v[32];
-        tmem_ld32(acc + (uint32_t)c0, v);
-        if (swiglu) {
-          float u[32];
-          tmem_ld32(acc + (uint32_t)(out_bn + c0), u);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
-        } else if (p.act == MOE_ACT_GELU) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
-        } else if (p.act == MOE_ACT_SILU) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
-        }
-        if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(crow + c0);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            __half2 h0 = __floats2half2_rn(v[8 * i + 0] * scale, v[8 * i + 1] * scale);
-            __half2 h1 = __floats2half2_rn(v[8 * i + 2] * scale, v[8 * i + 3] * scale);
-            __half2 h2 = __floats2half2_rn(v[8 * i + 4] * scale, v[8 * i + 5] * scale);
-            __half2 h3 = __floats2half2_rn(v[8 * i + 6] * scale, v[8 * i + 7] * scale);
-            uint4 o;
-            o.x = *reinterpret_cast<uint32_t*>(&h0);
-            o.y = *reinterpret_cast<uint32_t*>(&h1);
-            o.z = *reinterpret_cast<uint32_t*>(&h2);
-            o.w = *reinterpret_cast<uint32_t*>(&h3);
-            dst[i] = o;
-          }
-        }
+      if (out_bn % 32 == 0) {
+        for (int c0 = 0; c0 < out_bn; c0 += 32)
+          epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0);
+      } else {
+        for (int c0 = 0; c0 < out_bn; c0 += 16)
+          epilogue_chunk<16>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0);
       }
       tc_fence_before();
       mbar_arrive(tempty0 + 8 * ab);  // this thread is done reading the accumulator
@@ -272,7 +288,9 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   if (experts <= 0 || rows < 0 || K <= 0 || N <= 0) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad shape");
   if (experts > kMaxExperts) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: experts must be <= %d", kMaxExperts);
   if (K % 8 != 0) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: K must be a multiple of 8, got %d", K);
-  if (N % 64 != 0) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: N must be a multiple of 64, got %d", N);
+  if (N % 16 != 0) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: N must be a multiple of 16, got %d", N);
+  if (w_layout == MOE_W_KN && N % 64 != 0)
+    return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: N must be a multiple of 64 for [K,N] weights, got %d", N);
   if (activation < MOE_ACT_NONE || activation > MOE_ACT_SWIGLU) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad activation");
   if (w_layout != MOE_W_KN && w_layout != MOE_W_NK) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad weight layout");
   if (rows == 0) return MOE_OK;
@@ -284,7 +302,7 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   GParams p;
   p.offsets = offsets; p.experts = experts; p.rows = rows; p.K = K; p.n_out = N;
   // accumulator columns per tile; SwiGLU tiles hold `bn/2` gate and `bn/2` up columns
-  int out_bn = N % 256 == 0 ? 256 : (N % 128 == 0 ? 128 : 64);
+  int out_bn = N % 256 == 0 ? 256 : (N % 128 == 0 ? 128 : (N % 64 == 0 ? 64 : (N % 32 == 0 ? 32 : 16)));
   if (swiglu && out_bn > 128) out_bn = 128;
   p.bn = swiglu ? 2 * out_bn : out_bn;
   p.n_tiles = N / out_bn;

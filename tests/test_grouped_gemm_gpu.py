@@ -61,6 +61,10 @@ CASES = [
     ([33, 129, 0, 256], 320, 128, "kn", "swiglu"),
     ([40, 200, 0, 17], 256, 64, "kn", "silu"),
     ([0, 0, 0, 0], 128, 128, "nk", None),
+    ([24, 24, 7], 64, 32, "nk", None),
+    ([24, 24, 7], 32, 64, "nk", "swiglu"),
+    ([50, 3], 72, 48, "nk", "gelu"),
+    ([50, 3], 64, 16, "nk", "swiglu"),
 ]
 
 
