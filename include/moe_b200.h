@@ -98,6 +98,27 @@ int moe_pack(const void* x, int elem_bytes, const int32_t* idx, int tokens, int 
              int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * moe_pack for callers that cannot allocate.  (No counterpart in the reference.)
+ * Same inputs, outputs and ordering as moe_pack, but the scratch that moe_pack takes from a
+ * caller-owned workspace comes from a 256 KiB array built into the library image, so the call
+ * needs no cudaMalloc on anybody's side: meant for code that runs inside a fixed memory plan or
+ * inside a host hook where device allocation is forbidden or may stall the device.
+ *   - limits: tokens <= 8192 and experts <= 256; larger sizes return MOE_ERR_UNSUPPORTED
+ *     (use moe_pack);
+ *   - the call allocates and frees nothing, and calls no allocating library routine;
+ *   - the first call on each device looks up the array's device address (once, cached); make
+ *     that first call before any stream capture begins on that device;
+ *   - all calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *     (different streams without ordering between them) race; serialise them.  The array keeps
+ *     the last call's contents, and every word a call reads it has written first;
+ *   - device_status: NULL, or one int32 on the device that receives a non-zero code if an expert
+ *     index is out of range (the caller clears it).
+ */
+int moe_pack_static(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+                    int top_k, int32_t* counts, int32_t* offsets, void* packed, int32_t* row_route,
+                    int32_t* route_row, int32_t* device_status, void* stream);
+
+/*
  * Gate-weighted un-permute and sum over the top_k picks:
  *   out[t] = sum_j gates[t,j] * y[route_row[t*top_k + j]]   (fp32 accumulate)
  * Replaces: `expert(x_e) * w_e` + index_add_ (models/decoder_moe.py:270-271).

@@ -16,6 +16,7 @@
 // expert segment is ascending route id, run to run.  There is no host
 // synchronisation: total rows = tokens * top_k is known in advance.
 #include <cstdlib>
+#include <mutex>
 
 #include "sm100.cuh"
 
@@ -492,4 +493,85 @@ extern "C" int moe_pack(const void* x, int elem_bytes, const int32_t* idx, int t
   }
   return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, packed,
                              row_route, route_row, ws, s);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of moe_pack.
+//
+// Some callers cannot hand the library a workspace because they cannot allocate device memory at
+// the point of the call: code running under a memory plan fixed in advance (an inference engine
+// that has already carved up its arena), a plugin whose host forbids cudaMalloc inside its
+// execute hook, or a latency-critical loop where an allocator call may synchronise the device.
+// For them the tile histograms live in a fixed array that is part of the loaded library image.
+namespace moe {
+namespace {
+
+constexpr int kStaticMaxTokens = 8192;   // 256 tiles of 32 tokens
+constexpr int kStaticMaxExperts = 256;
+constexpr size_t kStaticScratchBytes =
+    (size_t)(kStaticMaxTokens / kTileTokens) * kStaticMaxExperts * sizeof(int32_t);  // 262,144 bytes
+
+// Held by every GPU that loads the library, until the process exits.
+static __device__ __align__(256) unsigned char g_pack_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; kernels need its device address, which is looked up
+// once per device (with that device current) and cached.
+int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_pack_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(MOE_ERR_UNSUPPORTED, "moe_pack_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_pack_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(MOE_ERR_LAUNCH, "moe_pack_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return MOE_OK;
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_pack_static(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+                               int top_k, int32_t* counts, int32_t* offsets, void* packed, int32_t* row_route,
+                               int32_t* route_row, int32_t* device_status, void* stream) {
+  using namespace moe;
+  if (tokens < 0 || d <= 0 || experts <= 0) return fail(MOE_ERR_ARG, "moe_pack_static: bad shape");
+  if (top_k < 1 || top_k > 8) return fail(MOE_ERR_UNSUPPORTED, "moe_pack_static: top_k must be in [1,8], got %d", top_k);
+  if (tokens > kStaticMaxTokens || experts > kStaticMaxExperts)
+    return fail(MOE_ERR_UNSUPPORTED,
+                "moe_pack_static: at most %d tokens and %d experts fit the built-in scratch (got %d, %d); "
+                "use moe_pack with a caller-owned workspace", kStaticMaxTokens, kStaticMaxExperts, tokens, experts);
+  if (elem_bytes != 2 && elem_bytes != 4) return fail(MOE_ERR_ARG, "moe_pack_static: elem_bytes must be 2 or 4");
+  if (!counts || !offsets) return fail(MOE_ERR_ARG, "moe_pack_static: null counts/offsets");
+  if (tokens > 0 && (!idx || !row_route || (packed && !x))) return fail(MOE_ERR_ARG, "moe_pack_static: null pointer");
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != MOE_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Workspace ws;
+  ws.status = device_status;  // may be null: errors are then not recorded
+  ws.control = nullptr;
+  ws.tile_hist = static_cast<int32_t*>(scratch);
+  ws.tile_base = nullptr;     // never used: at most 256 tiles, every scatter CTA sums the histograms
+  ws.fscratch = nullptr;
+  ws.num_tiles = num_tiles_for(tokens > 0 ? tokens : 1);
+  if (tokens > 0) {
+    // every histogram word that is read below is written here first: nothing in the array has to
+    // start at zero, whatever the previous call left behind
+    pack_hist_kernel<<<ws.num_tiles, 256, experts * sizeof(int32_t), s>>>(idx, ws.tile_hist, tokens, experts, top_k,
+                                                                         ws.status);
+    rc = check_launch("pack_hist_kernel");
+    if (rc != MOE_OK) return rc;
+  }
+  return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, packed, row_route,
+                             route_row, ws, s);
 }
