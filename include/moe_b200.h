@@ -191,6 +191,22 @@ int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offse
                      int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
                      const float* row_scale, void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Expert-parallel re-bucketing of rows received by the dispatch all-to-all.
+ * Replaces: the argsort / index_select / bincount bucketing of received rows
+ * (bench_2gpu_pcie.py:130-171) on the owner rank.
+ *   counts_all [world, experts] int32: the all-gathered per-rank route counts
+ *   src / dst  [rows, d]: forward (backward == 0) moves source-major rows
+ *              ([source rank][local expert][rows], what the all-to-all delivers) to expert-major
+ *              order ([local expert][source rank][rows], what moe_grouped_gemm reads) and writes
+ *              local_offsets int32 [experts/world + 1]; backward != 0 is the inverse move and
+ *              ignores local_offsets (may be NULL)
+ *   skip_src:  a source rank whose rows are not in the buffers (-1 for none): the rank itself,
+ *              when its own rows bypass the all-to-all (bench_2gpu_pcie.py:23-25)
+ */
+int moe_ep_rebucket(const void* src, void* dst, const int32_t* counts_all, int experts, int world, int rank,
+                    int skip_src, int backward, int d, int elem_bytes, int32_t* local_offsets, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

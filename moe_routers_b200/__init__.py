@@ -6,7 +6,7 @@ libmoe_b200.so on import; a missing library is an error, never a fallback.
 """
 import importlib
 
-_SUBMODULES = ("ops", "routers", "moe_layer", "fused_select_cuda", "grouped_ffn_cuda", "ep", "build", "_lib")
+_SUBMODULES = ("ops", "routers", "moe_layer", "fused_select_cuda", "grouped_ffn_cuda", "ep", "bench_ep", "bench_router", "strategies", "build", "_lib")
 
 
 def __getattr__(name):

@@ -147,18 +147,32 @@ sinkhorn_kernel(const SParams p) {
     }
     ok = grid_barrier(p.control, (int)gridDim.x, p.status, &s_flag);
     if (!ok) break;
+    // every CTA adds the partials of all CTAs in the same fixed order: `groups` threads per column
+    // each take a contiguous range of CTAs (loads in flight together), then the ranges are added
+    // in order
     const float* all = p.scratch + (size_t)(it & 1) * gridDim.x * E;
+    const int nblk = (int)gridDim.x;
+    const int per = (nblk + groups - 1) / groups;
+    if (g < groups) {
+      for (int j = jc; j < E; j += cw) {
+        const int c0 = g * per, c1 = min(nblk, c0 + per);
+        float s = 0.f;
+        int c = c0;
+        for (; c + 7 < c1; c += 8) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = __ldcg(all + (size_t)(c + u) * E + j);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) s += v[u];
+        }
+        for (; c < c1; ++c) s += __ldcg(all + (size_t)c * E + j);
+        s_part[(size_t)g * E + j] = s;
+      }
+    }
+    __syncthreads();
     for (int j = threadIdx.x; j < E; j += kThreads) {
       float s = 0.f;
-      int c = 0;
-      for (; c + 3 < (int)gridDim.x; c += 4) {
-        const float v0 = __ldcg(all + (size_t)(c + 0) * E + j);
-        const float v1 = __ldcg(all + (size_t)(c + 1) * E + j);
-        const float v2 = __ldcg(all + (size_t)(c + 2) * E + j);
-        const float v3 = __ldcg(all + (size_t)(c + 3) * E + j);
-        s = ((s + v0) + v1) + v2 + v3;
-      }
-      for (; c < (int)gridDim.x; ++c) s += __ldcg(all + (size_t)c * E + j);
+      for (int gg = 0; gg < groups; ++gg) s += s_part[(size_t)gg * E + j];
       const float b = s_b[j];
       s_b[j] = b / (b * s + p.eps) * ct;
     }
@@ -252,7 +266,7 @@ extern "C" int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, in
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
-  int grid = (tokens + 31) / 32;
+  int grid = (tokens + 127) / 128;  // about 128 rows per CTA: few partials to add after each barrier
   if (grid > sms) grid = sms;
   if (grid > kMaxGridBlocks) grid = kMaxGridBlocks;
   const int rows_per_cta = (tokens + grid - 1) / grid;

@@ -1,0 +1,61 @@
+"""The four routing strategies of the reference's router benchmark (bench_router.py:434-438,
+:468) as functions over the CUDA kernels: naive_topk, masked_matmul (A), fused_select (B),
+sinkhorn (C).  Each returns the routing of a batch; `moe_forward` / `masked_matmul_forward` run
+the expert FFNs on it (2-layer GELU FFN, weights [E, h, d] and [E, d, h])."""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+STRATEGIES = ["naive_topk", "masked_matmul", "fused_select", "sinkhorn"]
+
+
+def route(strategy: str, x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, skew_experts: int = 0,
+          skew_bias: float = 0.0, sinkhorn_iters: int = 10, sinkhorn_temperature: float = 1.0):
+    """Routing of `x` under `strategy`.  Returns a dict with idx / gates and, for the strategies that
+    permute (all but masked_matmul), counts / offsets / packed / row_route / route_row."""
+    e = w_router.size(0)
+    if strategy == "fused_select":
+        return ops.route_fused(x, w_router, top_k, skew_experts=skew_experts, skew_bias=skew_bias)
+    if strategy not in STRATEGIES:
+        raise ValueError(f"Unknown strategies: {[strategy]}. Valid: {STRATEGIES}")
+    idx, gates, logits = ops.router_gemm_select(x, w_router, top_k, skew_experts=skew_experts,
+                                                skew_bias=skew_bias, return_logits=True)
+    if strategy == "sinkhorn":
+        idx, gates = ops.sinkhorn(logits, top_k, iters=sinkhorn_iters, temperature=sinkhorn_temperature)
+    out = dict(idx=idx, gates=gates, logits=logits)
+    if strategy == "masked_matmul":
+        return out  # Strategy A: no permutation
+    counts, offsets, packed, row_route, route_row = ops.pack(x, idx, e)
+    out.update(counts=counts, offsets=offsets, packed=packed, row_route=row_route, route_row=route_row)
+    return out
+
+
+def moe_forward(r: dict, w1: torch.Tensor, w2: torch.Tensor, top_k: int, activation: str = "gelu") -> torch.Tensor:
+    """Sparse layer output from a routing with a packed buffer: grouped FFN + gate-weighted combine."""
+    h = ops.grouped_gemm(r["packed"], w1, r["offsets"], layout="nk", activation=activation)
+    y = ops.grouped_gemm(h, w2, r["offsets"], layout="nk")
+    return ops.combine(y, r["gates"], r["route_row"], top_k)
+
+
+def masked_matmul_forward(x: torch.Tensor, r: dict, w1: torch.Tensor, w2: torch.Tensor, top_k: int,
+                          activation: str = "gelu") -> torch.Tensor:
+    """Strategy A: every expert runs densely over ALL tokens; outputs are summed with the top-k gate
+    as mask (zero for unselected experts).  No permutation; E times the FLOPs of the sparse layer.
+    Limited to 8 experts (the combine kernel sums at most 8 rows per token)."""
+    t, d = x.shape
+    e = w1.size(0)
+    if e > 8:
+        raise RuntimeError("masked_matmul_forward supports at most 8 experts")
+    dev = x.device
+    seg = torch.tensor([0, t], dtype=torch.int32, device=dev)
+    y = torch.empty((e * t, d), dtype=x.dtype, device=dev)
+    for ex in range(e):  # one dense GEMM pair per expert, no host synchronisation
+        h = ops.grouped_gemm(x, w1[ex:ex + 1], seg, layout="nk", activation=activation)
+        ops.grouped_gemm(h, w2[ex:ex + 1], seg, layout="nk", out=y[ex * t:(ex + 1) * t])
+    dense = torch.zeros((t, e), dtype=torch.float32, device=dev)
+    dense.scatter_add_(1, r["idx"].long(), r["gates"])
+    rows = (torch.arange(e, device=dev, dtype=torch.int32).view(1, e) * t
+            + torch.arange(t, device=dev, dtype=torch.int32).view(t, 1)).contiguous()
+    return ops.combine(y, dense, rows.view(-1), e)

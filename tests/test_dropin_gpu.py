@@ -223,3 +223,33 @@ def test_moe_layer_matches_oracle(pkg, e, router):
     np.testing.assert_allclose(got, ref.astype(np.float32), rtol=2e-2, atol=2e-2 * scale)
     m = layer.get_last_metrics()
     assert m["tokens"] == 400 and int(m["route_counts"].sum()) == 400 * k
+
+
+@pytest.mark.parametrize("strategy", ["naive_topk", "fused_select", "sinkhorn", "masked_matmul"])
+def test_strategies_agree_with_oracle_layer(pkg, strategy):
+    """Benchmark configuration 3 in small: E=8, k=2, 2-layer GELU experts; every strategy's layer
+    output against the oracle evaluated on the routing the strategy chose."""
+    from moe_routers_b200 import strategies as S
+
+    t, d, h, e, k = 300, 256, 512, 8 if strategy == "masked_matmul" else 16, 2
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(t, d, generator=g).half()
+    w = (torch.randn(e, d, generator=g) / d ** 0.5).half()
+    w1 = (torch.randn(e, h, d, generator=g) / d ** 0.5).half()
+    w2 = (torch.randn(e, d, h, generator=g) / h ** 0.5).half()
+    r = S.route(strategy, x.cuda(), w.cuda(), k, skew_experts=2, skew_bias=1.0)
+    experts = {"w1": w1.numpy(), "w2": w2.numpy()}
+    idx, gates = r["idx"].cpu().numpy(), r["gates"].cpu().numpy()
+    if strategy == "masked_matmul":
+        out = S.masked_matmul_forward(x.cuda(), r, w1.cuda(), w2.cuda(), k)
+        ref = oracle.masked_matmul_layer(x.numpy(), idx, gates, experts, kind="gelu", layout="nk")
+        assert "packed" not in r
+    else:
+        out = S.moe_forward(r, w1.cuda(), w2.cuda(), k)
+        ref, _ = oracle.moe_layer(x.numpy(), idx, gates, experts, kind="gelu", layout="nk")
+    ref = ref.astype(np.float32)
+    scale = np.abs(ref).max()
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2 * scale)
+    if strategy in ("naive_topk", "masked_matmul"):
+        o = pkg.ops.route_fused(x.cuda(), w.cuda(), k, skew_experts=2, skew_bias=1.0)
+        assert torch.equal(o["idx"], r["idx"])  # same selection as the fused strategy

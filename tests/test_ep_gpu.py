@@ -1,0 +1,129 @@
+"""GPU tests of the expert-parallel layer: the re-bucket kernel against numpy, the layer on one
+rank, and (when the box has two GPUs) two NCCL ranks against the single-process oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_cuda(n=1):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} CUDA device(s)")
+
+
+@pytest.mark.parametrize("world,rank,e,d,skip", [(4, 1, 16, 64, 1), (2, 0, 8, 40, -1), (8, 7, 64, 128, 7), (1, 0, 4, 8, -1)])
+def test_rebucket_matches_numpy(world, rank, e, d, skip):
+    _need_cuda()
+    from moe_routers_b200 import _lib
+
+    el = e // world
+    rng = np.random.default_rng(world * 100 + rank)
+    counts_all = rng.integers(0, 40, size=(world, e)).astype(np.int32)
+    if world > 1:
+        counts_all[rng.integers(0, world), :] = 0  # a rank that sends nothing
+    lens = counts_all[:, rank * el:(rank + 1) * el].copy()  # [src, e_local]
+    if skip >= 0:
+        lens[skip] = 0
+    total = int(lens.sum())
+    src = rng.standard_normal((total, d)).astype(np.float16)
+    # expected expert-major order
+    a_off = np.concatenate([[0], np.cumsum(lens.reshape(-1))])
+    expect = np.concatenate([src[a_off[s * el + ee]:a_off[s * el + ee + 1]] for ee in range(el) for s in range(world)]
+                            + [np.zeros((0, d), np.float16)])
+    exp_off = np.concatenate([[0], np.cumsum(lens.sum(axis=0))]).astype(np.int32)
+
+    s_t = torch.from_numpy(src).cuda()
+    dst = torch.zeros_like(s_t)
+    back = torch.zeros_like(s_t)
+    c_t = torch.from_numpy(counts_all).cuda()
+    off_t = torch.full((el + 1,), -1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib.moe_ep_rebucket(s_t.data_ptr(), dst.data_ptr(), c_t.data_ptr(), e, world, rank, skip, 0, d, 2,
+                                        off_t.data_ptr(), st))
+    _lib.check(_lib.lib.moe_ep_rebucket(dst.data_ptr(), back.data_ptr(), c_t.data_ptr(), e, world, rank, skip, 1, d, 2,
+                                        None, st))
+    np.testing.assert_array_equal(dst.cpu().numpy(), expect)
+    np.testing.assert_array_equal(off_t.cpu().numpy(), exp_off)
+    np.testing.assert_array_equal(back.cpu().numpy(), src)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _ep_worker(rank, world, port, strategy, q):
+    try:
+        import torch.distributed as dist
+
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from moe_routers_b200.ep import EPMoELayer
+
+        t, d, h, e, k = 512 + 64 * rank, 256, 512, 16, 2
+        el = e // world
+        gw = torch.Generator().manual_seed(0)
+        w_router = (torch.randn(e, d, generator=gw) / d ** 0.5).half()
+        w1 = (torch.randn(e, h, d, generator=gw) / d ** 0.5).half()
+        w2 = (torch.randn(e, d, h, generator=gw) / h ** 0.5).half()
+        gx = torch.Generator().manual_seed(10 + rank)
+        x = torch.randn(t, d, generator=gx).half()
+        layer = EPMoELayer(w_router.cuda(), w1[rank * el:(rank + 1) * el].cuda().contiguous(),
+                           w2[rank * el:(rank + 1) * el].cuda().contiguous(), k, activation="gelu",
+                           strategy=strategy, skew_experts=4, skew_bias=2.0)
+        for overlap in (True, False):
+            out = layer(x.cuda(), overlap=overlap)
+            torch.cuda.synchronize()
+            o = layer.last["route"]
+            experts = {"w1": w1.numpy(), "w2": w2.numpy()}
+            ref, _ = oracle.moe_layer(x.numpy(), o["idx"].cpu().numpy(), o["gates"].cpu().numpy(), experts,
+                                      kind="gelu", layout="nk")
+            ref = ref.astype(np.float32)
+            scale = np.abs(ref).max()
+            # layer outputs: 2e-2 relative to the output scale (fp16)
+            np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2 * scale)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as exc:  # pragma: no cover
+        import traceback
+
+        q.put((rank, "".join(traceback.format_exception(exc))))
+
+
+def _run_ranks(world, strategy):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, strategy, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
+
+
+@pytest.mark.parametrize("strategy", ["fused_select", "sinkhorn"])
+def test_ep_layer_single_rank(strategy):
+    _need_cuda(1)
+    _run_ranks(1, strategy)
+
+
+@pytest.mark.parametrize("strategy", ["fused_select", "sinkhorn"])
+def test_ep_layer_two_ranks(strategy):
+    _need_cuda(2)
+    _run_ranks(2, strategy)
