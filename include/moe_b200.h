@@ -140,7 +140,7 @@ int moe_combine(const void* y, int dtype, const float* gates, const int32_t* rou
  *   logits_out: NULL or [tokens, experts] float32 receiving the values the
  *         selection saw
  *   remaining outputs as in moe_topk_select and moe_pack.
- * Limits: experts % 16 == 0, 16 <= experts <= 256, 1 <= top_k <= 8.
+ * Limits: experts <= 256, 1 <= top_k <= 8, top_k <= experts, d % 8 == 0.
  */
 int moe_route_fused(const void* x, const void* w_router, int tokens, int d, int experts, int top_k,
                     int skew_experts, float skew_bias, int32_t* idx, float* gates, int32_t* counts,

@@ -14,14 +14,13 @@
 // follows, and every CTA adds the partials in the same fixed order (bit-identical b everywhere,
 // run-to-run deterministic).  One grid barrier per iteration; the grid is launched cooperatively so
 // that all CTAs are co-resident, and the barrier spin is bounded in time.
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace moe {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr unsigned long long kBarrierLimitNs = 2000000000ull;
 
 struct SParams {
   const void* logits;
@@ -34,43 +33,6 @@ struct SParams {
   int32_t* control;  // [0] arrival count, [1] generation
   int32_t* status;
 };
-
-__device__ __forceinline__ int ld_acquire(const int32_t* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Generation barrier over the whole (co-resident) grid.  Returns false if the wait ran out.
-__device__ __forceinline__ bool grid_barrier(int32_t* control, int nblocks, int32_t* status, int* s_flag) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int ok = 1;
-    const int gen = ld_acquire(control + 1);
-    __threadfence();
-    const int prev = atomicAdd(control, 1);
-    if (prev == nblocks - 1) {
-      control[0] = 0;
-      __threadfence();
-      atomicAdd(control + 1, 1);
-    } else {
-      unsigned long long t0;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-      while (ld_acquire(control + 1) == gen) {
-        unsigned long long t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > kBarrierLimitNs) {
-          record_error(status, kErrGridBarrier);
-          ok = 0;
-          break;
-        }
-      }
-    }
-    *s_flag = ok;
-  }
-  __syncthreads();
-  return *s_flag != 0;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)

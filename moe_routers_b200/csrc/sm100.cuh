@@ -55,7 +55,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // block and returns false; the caller then skips its remaining work and
 // proceeds to the common exit path.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // fast path: poll without touching the global timer (reading it is slow)
+#pragma unroll 1
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
@@ -212,6 +215,50 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, f
 }
 
 }  // namespace sm100
+
+// ---- grid-wide barrier ---------------------------------------------------------------------
+// Generation barrier over a grid whose CTAs are all resident (cooperative launch).  control[0] is
+// the arrival count, control[1] the generation; both return to a consistent state after every use.
+// The spin is bounded in time: on expiry a code goes to the status block and every thread of the
+// CTA gets `false` (the barrier words are then stale: re-initialise the workspace).
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool grid_barrier(int32_t* control, int nblocks, int32_t* status, int* s_flag) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const int gen = ld_acquire_gpu(control + 1);
+    __threadfence();
+    const int prev = atomicAdd(control, 1);
+    if (prev == nblocks - 1) {
+      control[0] = 0;
+      __threadfence();
+      atomicAdd(control + 1, 1);
+    } else {
+      // poll in bursts; the (slow) global timer is only read between bursts
+      bool released = false;
+      for (int i = 0; i < 4096 && !released; ++i) released = ld_acquire_gpu(control + 1) != gen;
+      if (!released) {
+        const unsigned long long t0 = sm100::globaltimer_ns();
+        while (!released) {
+#pragma unroll 1
+          for (int i = 0; i < 1024 && !released; ++i) released = ld_acquire_gpu(control + 1) != gen;
+          if (!released && sm100::globaltimer_ns() - t0 > sm100::kWaitLimitNs) {
+            record_error(status, kErrGridBarrier);
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+    *s_flag = ok;
+  }
+  __syncthreads();
+  return *s_flag != 0;
+}
 
 // ---- host: tensor maps ----------------------------------------------------------
 // Encode a 2-D row-major fp16/bf16 tensor [rows, cols] (cols contiguous) with a

@@ -85,8 +85,7 @@ class MoELayer(torch.nn.Module):
             raise RuntimeError("x must be fp16 (Half)")
         flat = x.reshape(-1, d_model)
         e, k = self.n_experts, self.top_k
-        fused = (type(self.router_impl) is CUDATopKRouter and e % 16 == 0 and 16 <= e <= 256
-                 and k <= 8 and d_model % 8 == 0)
+        fused = type(self.router_impl) is CUDATopKRouter and e <= 256 and k <= 8 and d_model % 8 == 0
         if fused:
             o = ops.route_fused(flat, self.router.weight, k)
             gates, packed, offsets, route_row, counts = o["gates"], o["packed"], o["offsets"], o["route_row"], o["counts"]

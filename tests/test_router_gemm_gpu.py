@@ -29,6 +29,7 @@ SHAPES = [
     (4096, 4096, 64, 2, 8, 2.0), (4096, 4096, 64, 2, 0, 0.0), (1000, 512, 64, 2, 8, 2.0),
     (130, 64, 16, 1, 0, 0.0), (257, 4096, 128, 4, 3, -1.5), (64, 200, 32, 2, 0, 0.0),
     (300, 1024, 256, 8, 16, 0.5), (1, 4096, 64, 2, 0, 0.0), (127, 136, 48, 3, 0, 0.0),
+    (4096, 4096, 8, 2, 0, 0.0), (333, 512, 40, 5, 3, 1.0), (64, 64, 2, 2, 0, 0.0),
 ]
 
 
@@ -57,7 +58,9 @@ def test_router_gemm_select(ops, t, d, e, k, skew_n, skew_b):
     np.testing.assert_array_equal(idx.cpu().numpy()[rows], o_idx[rows].astype(np.int32))
 
 
-@pytest.mark.parametrize("t,d,e,k,skew_n,skew_b", SHAPES[:5] + [(0, 64, 64, 2, 0, 0.0)])
+@pytest.mark.parametrize("t,d,e,k,skew_n,skew_b", SHAPES[:5] + [(0, 64, 64, 2, 0, 0.0), (4736, 1024, 64, 2, 8, 2.0),
+                                                    (5000, 1024, 64, 2, 0, 0.0), (31, 2048, 64, 8, 0, 0.0),
+                                                    (1000, 8192, 32, 2, 0, 0.0), (513, 1024, 256, 3, 0, 0.0)])
 def test_route_fused(ops, t, d, e, k, skew_n, skew_b):
     x, w = _inputs(t, d, e, 5 + t + d + e)
     o = ops.route_fused(x.cuda(), w.cuda(), k, skew_experts=skew_n, skew_bias=skew_b, return_logits=t > 0)
