@@ -37,6 +37,10 @@ T, D, E, K_TOP = 4096, 4096, 64, 2
 SKEW_N, SKEW_B = 8, 2.0
 ROUTE_BYTES = T * D * 2 + E * D * 2 + K_TOP * T * D * 2 + 2 * T * K_TOP * 4 + E * 4 + (E + 1) * 4  # 101,253,636
 PACK_BYTES = T * D * 2 + T * K_TOP * 4 + K_TOP * T * D * 2  # 100,696,064
+# dram__bytes_read.sum + dram__bytes_write.sum of one scatter launch at this size, from the ncu capture
+# summarised in profiles/pack_scatter_bulk_T4096_d4096_E64_k2.md (the L2 still holds most of the
+# 67 MB written when the kernel ends, hence less than the algorithmic bytes)
+SCATTER_DRAM_TRAFFIC = 42_600_000
 WORKLOAD = "fused_select T=4096 d_model=4096 E=64 top_k=2 fp16, +2.0 skew on experts 0..7"
 
 
@@ -171,6 +175,14 @@ def main_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    else:  # the expert-parallel layer below runs through torch.distributed even on one rank
+        import socket
+
+        sock = socket.socket()
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+        sock.close()
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1, device_id=dev)
 
     from moe_routers_b200 import ops  # raises if libmoe_b200.so is missing: there is no fallback
 
@@ -278,6 +290,27 @@ def main_ours(args):
     h2d = x_host.numel() * 2 + w_host.numel() * 2
     d2h = sum(v.numel() * v.element_size() for v in host_out.values())
 
+    # ---- the expert-parallel MoE layer on the same ranks (T=4096 tokens per rank, 64 experts split
+    # over the ranks, 2-layer GELU experts 4096 -> 8192 -> 4096), skewed and unskewed -------------
+    ep = {}
+    try:
+        import argparse as _ap
+
+        from moe_routers_b200 import bench_ep
+
+        del xs, sel_outs
+        torch.cuda.empty_cache()
+        for tag, (sn, sb) in {"skew": (SKEW_N, SKEW_B), "plain": (0, 0.0)}.items():
+            ns = _ap.Namespace(experts=E, top_k=K_TOP, d_model=D, hidden=8192, tokens=T, all_strategies=False,
+                               strategies=["fused_select"], strategy="fused_select", sinkhorn_iters=10,
+                               sinkhorn_temperature=1.0, warmup=2, iters=5, skew_experts=sn, skew_bias=sb)
+            r = bench_ep.run(ns)[0]
+            ep[tag] = {k: r[k] for k in ("t_route_us", "t_comm_us", "t_comp_us", "t_combine_us", "t_layer_seq_us",
+                                         "t_layer_overlap_us", "eta_overlap", "load_max_over_mean", "load_cv",
+                                         "tokens_per_s")}
+    except Exception as exc:  # the route numbers above stand on their own
+        ep = {"error": f"{type(exc).__name__}: {exc}"}
+
     # sanity: the result of the last step agrees with the invariants of the route
     o = outs[0]
     assert int(o["offsets"][-1]) == T * K_TOP and int(o["counts"].sum()) == T * K_TOP
@@ -294,7 +327,7 @@ def main_ours(args):
                        "launch": "K steps captured in one CUDA graph"},
             "breakdown_us": {"t_logit_select": select_us, "t_pack": scatter_us, "t_route": ms_per_step * 1e3},
             "roofline": {"kernel": "pack_scatter_bulk_kernel", "bound": "hbm", "achieved": pack_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": pack_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "unit": "GB/s", "frac": pack_gbs / peak, "traffic": SCATTER_DRAM_TRAFFIC, "peak_kind": peak_kind,
                          "algorithmic_bytes": PACK_BYTES,
                          "duration_us": scatter_us, "how": "events: K fused steps minus K router-kernel-only steps"},
             "route_roofline": {"bound": "hbm", "achieved": route_gbs, "peak": peak, "unit": "GB/s",
@@ -303,14 +336,14 @@ def main_ours(args):
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
             "gpu_launches": 2 * steps,
             "clocks": sampler.summary(),
+            "ep_layer": ep,
         }
         if cpu is not None:
             line["cpu_baseline"] = {"value": cpu["value"], "unit": "tokens/s", "cores": cpu["cores"], "kind": "port",
                                     "sample": "3 full passes of T=4096 tokens (fp32, naive_topk path)",
                                     "breakdown_ms": cpu["breakdown_ms"]}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

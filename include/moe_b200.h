@@ -184,12 +184,15 @@ int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, int experts, 
  *   c = silu(gate) * up has N columns)
  *   offsets [experts+1] int32 on the device; `rows` is the capacity of a / c
  *   row_scale: NULL or float32 [rows] multiplied into the result rows.
+ *   sm_margin: SMs the persistent grid leaves free (0 = use all), so that a communication
+ *              kernel running on another stream can make progress next to it.
  * Limits: K % 8 == 0; N % 16 == 0 for [N,K] weights, N % 64 == 0 for [K,N] weights;
  * experts <= 1024.
  */
 int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts,
                      int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
-                     const float* row_scale, void* workspace, size_t workspace_bytes, void* stream);
+                     const float* row_scale, int sm_margin, void* workspace, size_t workspace_bytes,
+                     void* stream);
 
 /*
  * Expert-parallel re-bucketing of rows received by the dispatch all-to-all.
@@ -203,9 +206,13 @@ int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offse
  *              ignores local_offsets (may be NULL)
  *   skip_src:  a source rank whose rows are not in the buffers (-1 for none): the rank itself,
  *              when its own rows bypass the all-to-all (bench_2gpu_pcie.py:23-25)
+ *   first_local_expert, num_local_experts: the range of this rank's experts the buffers hold (the
+ *              layer exchanges and computes the local experts in chunks so that the exchange of one
+ *              chunk overlaps the FFN of another); local_offsets then has num_local_experts + 1 entries
  */
 int moe_ep_rebucket(const void* src, void* dst, const int32_t* counts_all, int experts, int world, int rank,
-                    int skip_src, int backward, int d, int elem_bytes, int32_t* local_offsets, void* stream);
+                    int skip_src, int backward, int d, int elem_bytes, int first_local_expert,
+                    int num_local_experts, int32_t* local_offsets, void* stream);
 
 #ifdef __cplusplus
 }

@@ -33,9 +33,9 @@ SIGNATURES = {
     "moe_combine": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _p]),
     "moe_route_fused": (_i, [_p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "moe_router_gemm_select": (_i, [_p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _sz, _p]),
-    "moe_ep_rebucket": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p]),
+    "moe_ep_rebucket": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p]),
     "moe_sinkhorn": (_i, [_p, _i, _i, _i, _i, _i, _f, _f, _p, _p, _p, _sz, _p]),
-    "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _sz, _p]),
+    "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _i, _p, _sz, _p]),
 }
 
 

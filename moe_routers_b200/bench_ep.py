@@ -37,7 +37,7 @@ def _event_us(fn, stream=None) -> float:
 
 def run(args) -> list[dict]:
     from . import ops
-    from .ep import EPMoELayer, plan_exchange, split_rows
+    from .ep import EPMoELayer
 
     rank, world = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -71,31 +71,15 @@ def run(args) -> list[dict]:
             acc["route"] += _event_us(lambda: out.update(o=layer.route(x)))
             o = out["o"]
             counts_all, counts_host = layer.exchange_counts(o["counts"])
-            send, recv = plan_exchange(counts_host, rank, world)
-            off = [0] + [int(v) for v in counts_host[rank].to(torch.int64).cumsum(0).tolist()]
-            packed = o["packed"]
-            y_packed = torch.empty_like(packed)
-            dest = [packed[off[p * el]:off[(p + 1) * el]] for p in range(world)]
-            ret = [y_packed[off[p * el]:off[(p + 1) * el]] for p in range(world)]
-            recv_buf = torch.empty((sum(recv), d), dtype=x.dtype, device=dev)
-            ret_buf = torch.empty_like(recv_buf)
-            bucketed = torch.empty_like(recv_buf)
-            y_b = torch.empty_like(recv_buf)
-            remote_off = torch.zeros(el + 1, dtype=torch.int32, device=dev)
-            lo, hi = off[rank * el], off[(rank + 1) * el]
-            local_off = (o["offsets"][rank * el:(rank + 1) * el + 1] - o["offsets"][rank * el]).contiguous()
+            pl = layer.plan(o, counts_all, counts_host, 1)
+            y_packed = pl["y_packed"]
 
             def comm():
-                layer._exchange(dest, split_rows(recv_buf, recv))
-                layer._exchange(split_rows(ret_buf, recv), ret)
+                layer.dispatch(pl, 0)
+                layer.give_back(pl, 0)
 
             def comp():
-                if hi > lo:
-                    layer._ffn(packed[lo:hi], local_off, y_packed[lo:hi])
-                if recv_buf.size(0) > 0:
-                    layer._rebucket(recv_buf, bucketed, counts_all, False, remote_off)
-                    layer._ffn(bucketed, remote_off, y_b)
-                    layer._rebucket(y_b, ret_buf, counts_all, True, None)
+                layer.compute(pl, 0)
 
             dist.barrier()
             acc["comm"] += _event_us(comm)
@@ -120,7 +104,7 @@ def run(args) -> list[dict]:
             eta_overlap=(t_route + t_comm + t_comp + t_combine) / max(t_ovl, 1e-6),
             load_max_over_mean=float(counts.max() / (mean + 1e-9)),
             load_cv=float(counts.std(unbiased=False) / (mean + 1e-9)),
-            rows_received_rank0=int(sum(layer.last["recv"])) if rank == 0 else None,
+            rows_received_rank0=int(sum(sum(r_) for r_ in layer.last["plan"]["rows"])) if rank == 0 else None,
             tokens_per_s=world * t / (t_ovl * 1e-6),
         ))
     return results

@@ -18,17 +18,17 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads)
 ep_rebucket_kernel(const char* __restrict__ src, char* __restrict__ dst, const int32_t* __restrict__ counts_all,
                    int experts, int world, int rank, int skip_src, int backward, size_t row_bytes,
-                   int32_t* __restrict__ local_offsets) {
+                   int e_lo, int el, int32_t* __restrict__ local_offsets) {
   __shared__ int s_a, s_b, s_len;
-  const int el = experts / world;
-  const int seg = blockIdx.x;  // seg = s * el + e
+  const int e_base = rank * (experts / world) + e_lo;  // first global expert of the range
+  const int seg = blockIdx.x;  // seg = s * el + e  (e counts inside the range)
   const int s = seg / el, e = seg % el;
   if (threadIdx.x < 32) {
     // A = rows before (s, e) in source-major order, B = rows before it in expert-major order
     int a = 0, b = 0, len = 0, total = 0;
     for (int i = threadIdx.x; i < world * el; i += 32) {
       const int ss = i / el, ee = i % el;
-      const int l = (ss == skip_src) ? 0 : counts_all[(size_t)ss * experts + rank * el + ee];
+      const int l = (ss == skip_src) ? 0 : counts_all[(size_t)ss * experts + e_base + ee];
       if (ss < s || (ss == s && ee < e)) a += l;
       if (ee < e || (ee == e && ss < s)) b += l;
       if (ss == s && ee == e) len = l;
@@ -78,18 +78,21 @@ ep_rebucket_kernel(const char* __restrict__ src, char* __restrict__ dst, const i
 }  // namespace moe
 
 extern "C" int moe_ep_rebucket(const void* src, void* dst, const int32_t* counts_all, int experts, int world,
-                               int rank, int skip_src, int backward, int d, int elem_bytes,
-                               int32_t* local_offsets, void* stream) {
+                               int rank, int skip_src, int backward, int d, int elem_bytes, int first_local_expert,
+                               int num_local_experts, int32_t* local_offsets, void* stream) {
   using namespace moe;
   if (experts <= 0 || world <= 0 || experts % world != 0)
     return fail(MOE_ERR_ARG, "experts must be divisible by world_size");
   if (rank < 0 || rank >= world) return fail(MOE_ERR_ARG, "moe_ep_rebucket: bad rank");
   if (d <= 0 || (elem_bytes != 2 && elem_bytes != 4)) return fail(MOE_ERR_ARG, "moe_ep_rebucket: bad row shape");
   if (!src || !dst || !counts_all) return fail(MOE_ERR_ARG, "moe_ep_rebucket: null pointer");
-  const int segs = experts;  // world * (experts / world)
+  const int el_all = experts / world;
+  if (first_local_expert < 0 || num_local_experts <= 0 || first_local_expert + num_local_experts > el_all)
+    return fail(MOE_ERR_ARG, "moe_ep_rebucket: bad local expert range");
+  const int segs = world * num_local_experts;
   dim3 grid(segs, 16, 1);
   ep_rebucket_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const char*>(src), static_cast<char*>(dst), counts_all, experts, world, rank, skip_src,
-      backward ? 1 : 0, (size_t)d * elem_bytes, local_offsets);
+      backward ? 1 : 0, (size_t)d * elem_bytes, first_local_expert, num_local_experts, local_offsets);
   return check_launch("ep_rebucket_kernel");
 }

@@ -283,7 +283,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts, int rows,
                                 int K, int N, int w_layout, int64_t stride_w, int activation,
-                                const float* row_scale, void* workspace, size_t workspace_bytes, void* stream) {
+                                const float* row_scale, int sm_margin, void* workspace, size_t workspace_bytes,
+                                void* stream) {
   using namespace moe;
   if (experts <= 0 || rows < 0 || K <= 0 || N <= 0) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad shape");
   if (experts > kMaxExperts) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: experts must be <= %d", kMaxExperts);
@@ -338,6 +339,7 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
+  if (sm_margin > 0 && sm_margin < sms) sms -= sm_margin;
   // upper bound of the tile count known on the host: every expert may add one partial m tile
   const long long max_tiles = ((long long)rows / kBM + experts) * p.n_tiles;
   const int grid = (int)(max_tiles < sms ? max_tiles : sms);

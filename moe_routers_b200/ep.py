@@ -5,12 +5,12 @@ size W that divides the expert count, and completes it with the combine step the
 
     route (logit GEMM + select + pack)        every rank on its own tokens            [CUDA]
     all-gather of the per-expert counts        256 B per rank, one host read           [NCCL]
-    dispatch all-to-all of the packed rows     remote rows only, self split = 0        [NCCL, comm stream]
-    expert FFN on the rank's own rows          overlaps the dispatch                   [CUDA, main stream]
-    re-bucket received rows by local expert    source-major -> expert-major            [CUDA]
-    expert FFN on the received rows
-    re-bucket back, combine all-to-all         rows return in the order they were sent [NCCL]
-    gate-weighted combine                                                               [CUDA]
+    for each group c of the local experts (pipelined, exchanges on a second stream):
+      dispatch all-to-all of the packed rows   grouped send/recv straight from `packed` [NCCL]
+      re-bucket received rows by local expert  source-major -> expert-major             [CUDA]
+      expert FFN (grouped GEMM x2)             every expert's weights are read once     [CUDA]
+      re-bucket back, combine all-to-all       rows return to the slot they came from   [NCCL]
+    gate-weighted combine                                                                [CUDA]
 
 Experts are split contiguously: owner(e) = e // (E / W) (bench_2gpu_pcie.py:216-219, :372).  The
 packed buffer is expert-sorted, so the rows for destination r are one slice of it and the send
@@ -103,6 +103,13 @@ class EPMoELayer:
         self.sinkhorn_iters, self.sinkhorn_temperature = sinkhorn_iters, sinkhorn_temperature
         self.skew_experts, self.skew_bias = skew_experts, skew_bias
         self.comm_stream = torch.cuda.Stream()
+        # Expert groups pipelined against the exchanges, and SMs the persistent GEMM leaves to the
+        # exchange kernels while it runs.  Measured on 2 B200s (T=4096/rank, d=4096, h=8192, E=64):
+        # one group with no margin is fastest (1.95 ms); 2 groups / 16 SMs costs more in GEMM wave
+        # tails and lost SMs (2.2 ms) than the ~0.09 ms per exchange it hides.  Raise both where the
+        # exchange is a larger share of the layer.
+        self.chunks = 1
+        self.sm_margin = 0
         self.last = {}
 
     # ---- stages (each usable on its own by the benchmark) -----------------------------------
@@ -124,13 +131,16 @@ class EPMoELayer:
         dist.all_gather_into_tensor(all_counts, counts, group=self.group)
         return all_counts, all_counts.cpu()
 
-    def _ffn(self, rows, offsets, out):
-        h = ops.grouped_gemm(rows, self.w1, offsets, layout="nk", activation=self.activation)
-        return ops.grouped_gemm(h, self.w2, offsets, layout="nk", out=out)
+    def _ffn(self, rows, offsets, out, e_lo=0, e_cnt=None, sm_margin=0):
+        e_hi = self.el if e_cnt is None else e_lo + e_cnt
+        h = ops.grouped_gemm(rows, self.w1[e_lo:e_hi], offsets, layout="nk", activation=self.activation,
+                             sm_margin=sm_margin)
+        return ops.grouped_gemm(h, self.w2[e_lo:e_hi], offsets, layout="nk", out=out, sm_margin=sm_margin)
 
-    def _rebucket(self, src, dst, counts_all, backward, local_offsets):
+    def _rebucket(self, src, dst, counts_all, backward, local_offsets, e_lo, e_cnt):
         check(lib.moe_ep_rebucket(src.data_ptr(), dst.data_ptr(), counts_all.data_ptr(), self.e, self.world,
-                                  self.rank, self.rank, 1 if backward else 0, src.size(1), src.element_size(),
+                                  self.rank, -1, 1 if backward else 0, src.size(1), src.element_size(),
+                                  int(e_lo), int(e_cnt),
                                   local_offsets.data_ptr() if local_offsets is not None else None,
                                   torch.cuda.current_stream().cuda_stream))
 
@@ -139,51 +149,93 @@ class EPMoELayer:
 
     _slices = staticmethod(split_rows)
 
-    # ---- the layer --------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, *, overlap: bool = True) -> torch.Tensor:
+    # ---- the layer, in stages ---------------------------------------------------------------
+    def plan(self, o, counts_all, counts_host, chunks: int):
+        """Buffers and slices of one forward pass.  The local experts are handled in `chunks` groups:
+        the exchange of one group overlaps the FFN of another, and every expert's weights are read
+        once.  Rows for (destination p, group c) are one slice of the expert-sorted packed buffer."""
+        r, el, w = self.rank, self.el, self.world
+        if chunks < 1 or el % chunks != 0:
+            chunks = 1
+        ec = el // chunks
+        packed = o["packed"]
+        d = packed.size(1)
+        off = [0] + [int(v) for v in counts_host[r].to(torch.int64).cumsum(0).tolist()]
+        cnt = counts_host.view(w, w, chunks, ec).sum(dim=3)  # [src, dst, chunk] rows
+        y_packed = torch.empty_like(packed)
+        pl = dict(o=o, counts_all=counts_all, chunks=chunks, ec=ec, y_packed=y_packed, send=[], back=[], recv=[],
+                  recv_buf=[], ret_buf=[], rows=[])
+        for c in range(chunks):
+            rows_from = [int(cnt[s_, r, c]) for s_ in range(w)]
+            recv_buf = torch.empty((sum(rows_from), d), dtype=packed.dtype, device=packed.device)
+            ret_buf = torch.empty_like(recv_buf)
+            lohi = [(off[p * el + c * ec], off[p * el + (c + 1) * ec]) for p in range(w)]
+            pl["send"].append([packed[lo:hi] for lo, hi in lohi])
+            pl["back"].append([y_packed[lo:hi] for lo, hi in lohi])
+            pl["recv"].append(split_rows(recv_buf, rows_from))
+            pl["recv_buf"].append(recv_buf)
+            pl["ret_buf"].append(ret_buf)
+            pl["rows"].append(rows_from)
+        return pl
+
+    def dispatch(self, pl, c):
+        """Rows of expert group c go to their owners (the rank's own rows by a device copy)."""
+        r = self.rank
+        if pl["recv"][c][r].numel():
+            pl["recv"][c][r].copy_(pl["send"][c][r])
+        self._exchange(pl["send"][c], pl["recv"][c])
+
+    def compute(self, pl, c, sm_margin=0):
+        """Bucket the received rows of group c by expert, run the expert FFN, restore arrival order."""
+        recv_buf = pl["recv_buf"][c]
+        if recv_buf.size(0) == 0:
+            return
+        ec = pl["ec"]
+        bucketed = torch.empty_like(recv_buf)
+        loc_off = torch.empty(ec + 1, dtype=torch.int32, device=recv_buf.device)
+        self._rebucket(recv_buf, bucketed, pl["counts_all"], False, loc_off, c * ec, ec)
+        y_b = self._ffn(bucketed, loc_off, torch.empty_like(bucketed), c * ec, ec, sm_margin)
+        self._rebucket(y_b, pl["ret_buf"][c], pl["counts_all"], True, None, c * ec, ec)
+
+    def give_back(self, pl, c):
+        """Combine exchange of group c: every result row returns to the packed slot it came from."""
+        r = self.rank
+        ret = split_rows(pl["ret_buf"][c], pl["rows"][c])
+        if ret[r].numel():
+            pl["back"][c][r].copy_(ret[r])
+        self._exchange(ret, pl["back"][c])
+
+    def forward(self, x: torch.Tensor, *, overlap: bool = True, chunks: Optional[int] = None) -> torch.Tensor:
         if not x.is_cuda:
             raise RuntimeError("inputs must be CUDA")
         main = torch.cuda.current_stream()
         comm = self.comm_stream if overlap else main
-        r, el, d = self.rank, self.el, x.size(1)
+        if chunks is None:
+            chunks = self.chunks if overlap else 1
+        margin = self.sm_margin if overlap else 0
 
         o = self.route(x)
         counts_all, counts_host = self.exchange_counts(o["counts"])
-        send, recv = plan_exchange(counts_host, r, self.world)
-        off = [0] + [int(v) for v in counts_host[r].to(torch.int64).cumsum(0).tolist()]
-        packed = o["packed"]
-        y_packed = torch.empty_like(packed)
-        # rows for destination p are packed[off[p*el] : off[(p+1)*el]]
-        dest_slices = [packed[off[p * el]:off[(p + 1) * el]] for p in range(self.world)]
-        ret_slices = [y_packed[off[p * el]:off[(p + 1) * el]] for p in range(self.world)]
-        recv_buf = torch.empty((sum(recv), d), dtype=x.dtype, device=x.device)
-        ret_buf = torch.empty_like(recv_buf)
-
-        # dispatch of the remote rows on the communication stream ...
+        pl = self.plan(o, counts_all, counts_host, chunks)
+        n = pl["chunks"]
+        arrived = [torch.cuda.Event() for _ in range(n)]
+        computed = [torch.cuda.Event() for _ in range(n)]
         comm.wait_stream(main)
         with torch.cuda.stream(comm):
-            self._exchange(dest_slices, self._slices(recv_buf, recv))
-        # ... while the rank's own rows (already expert-sorted for its experts) go through the FFN
-        lo, hi = off[r * el], off[(r + 1) * el]
-        if hi > lo:
-            local_off = (o["offsets"][r * el:(r + 1) * el + 1] - o["offsets"][r * el]).contiguous()
-            self._ffn(packed[lo:hi], local_off, y_packed[lo:hi])
-
-        # received rows: bucket by local expert, FFN, restore the order they arrived in
-        main.wait_stream(comm)
-        if recv_buf.size(0) > 0:
-            bucketed = torch.empty_like(recv_buf)
-            remote_off = torch.empty(el + 1, dtype=torch.int32, device=x.device)
-            self._rebucket(recv_buf, bucketed, counts_all, False, remote_off)
-            y_b = self._ffn(bucketed, remote_off, torch.empty_like(bucketed))
-            self._rebucket(y_b, ret_buf, counts_all, True, None)
-        # combine all-to-all: every result row returns to the packed position it was sent from
-        comm.wait_stream(main)
+            for c in range(n):
+                self.dispatch(pl, c)
+                arrived[c].record(comm)
+        for c in range(n):
+            main.wait_event(arrived[c])
+            self.compute(pl, c, margin)
+            computed[c].record(main)
         with torch.cuda.stream(comm):
-            self._exchange(self._slices(ret_buf, recv), ret_slices)
+            for c in range(n):
+                comm.wait_event(computed[c])
+                self.give_back(pl, c)
         main.wait_stream(comm)
-        out = ops.combine(y_packed, o["gates"], o["route_row"], self.k)
-        self.last = dict(counts_all=counts_host, send=send, recv=recv, route=o)
+        out = ops.combine(pl["y_packed"], o["gates"], o["route_row"], self.k)
+        self.last = dict(counts_all=counts_host, route=o, plan=pl)
         return out
 
     __call__ = forward

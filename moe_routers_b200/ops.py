@@ -204,7 +204,7 @@ _ACT = {None: _lib.MOE_ACT_NONE, "none": _lib.MOE_ACT_NONE, "gelu": _lib.MOE_ACT
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, layout: str = "nk",
                  activation: Optional[str] = None, row_scale: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, sm_margin: int = 0) -> torch.Tensor:
     """c[offsets[e]:offsets[e+1]] = act(a[offsets[e]:offsets[e+1]] @ W[e]) for every expert.
 
     a [rows, K] fp16; w [E, N, K] (layout "nk") or [E, K, N] (layout "kn"), fp16;
@@ -233,6 +233,6 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, lay
         rs = row_scale.to(torch.float32).contiguous() if row_scale is not None else None
         check(lib.moe_grouped_gemm(a.data_ptr(), w.data_ptr(), c.data_ptr(), offsets.data_ptr(), e, rows,
                                    k_dim, n_out, _lib.MOE_W_NK if layout == "nk" else _lib.MOE_W_KN,
-                                   w.stride(0), act, rs.data_ptr() if rs is not None else None,
+                                   w.stride(0), act, rs.data_ptr() if rs is not None else None, int(sm_margin),
                                    ws.data_ptr(), ws.numel(), _stream()))
     return c

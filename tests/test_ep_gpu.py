@@ -45,9 +45,9 @@ def test_rebucket_matches_numpy(world, rank, e, d, skip):
     off_t = torch.full((el + 1,), -1, dtype=torch.int32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
     _lib.check(_lib.lib.moe_ep_rebucket(s_t.data_ptr(), dst.data_ptr(), c_t.data_ptr(), e, world, rank, skip, 0, d, 2,
-                                        off_t.data_ptr(), st))
+                                        0, el, off_t.data_ptr(), st))
     _lib.check(_lib.lib.moe_ep_rebucket(dst.data_ptr(), back.data_ptr(), c_t.data_ptr(), e, world, rank, skip, 1, d, 2,
-                                        None, st))
+                                        0, el, None, st))
     np.testing.assert_array_equal(dst.cpu().numpy(), expect)
     np.testing.assert_array_equal(off_t.cpu().numpy(), exp_off)
     np.testing.assert_array_equal(back.cpu().numpy(), src)
