@@ -303,7 +303,7 @@ def main_ours(args):
         for tag, (sn, sb) in {"skew": (SKEW_N, SKEW_B), "plain": (0, 0.0)}.items():
             ns = _ap.Namespace(experts=E, top_k=K_TOP, d_model=D, hidden=8192, tokens=T, all_strategies=False,
                                strategies=["fused_select"], strategy="fused_select", sinkhorn_iters=10,
-                               sinkhorn_temperature=1.0, warmup=2, iters=5, skew_experts=sn, skew_bias=sb)
+                               sinkhorn_temperature=1.0, warmup=2, iters=5, skew_experts=sn, skew_bias=sb, transport="peer")
             r = bench_ep.run(ns)[0]
             ep[tag] = {k: r[k] for k in ("t_route_us", "t_comm_us", "t_comp_us", "t_combine_us", "t_layer_seq_us",
                                          "t_layer_overlap_us", "eta_overlap", "load_max_over_mean", "load_cv",

@@ -214,6 +214,35 @@ int moe_ep_rebucket(const void* src, void* dst, const int32_t* counts_all, int e
                     int skip_src, int backward, int d, int elem_bytes, int first_local_expert,
                     int num_local_experts, int32_t* local_offsets, void* stream);
 
+/*
+ * Device-initiated dispatch (combine == 0) and combine (combine != 0) over peer memory.
+ * Replaces: the all_to_all_single exchanges of rows and expert ids plus the receiver-side
+ * bucketing (bench_2gpu_pcie.py:460-488, :130-171).
+ *   peer_bufs: DEVICE array of `world` pointers; entry p is rank p's inbox (dispatch) or rank p's
+ *              packed-order result buffer (combine), mapped into this process (CUDA IPC); the
+ *              entry for the rank itself is its own buffer.  All must be 16-byte aligned.
+ *   dispatch:  local = this rank's packed rows; every expert segment is stored into its owner's
+ *              inbox at its expert-major position, so the owner's rows arrive already grouped by
+ *              expert; local_offsets (int32 [experts/world + 1]) receives this rank's own inbox
+ *              offsets for moe_grouped_gemm.
+ *   combine:   local = this rank's expert-major FFN output; every segment is stored into the packed
+ *              slot of the rank it came from.
+ * The kernel only stores; the caller orders the phases across ranks (every rank must have finished
+ * its dispatch before any rank reads its inbox, and likewise for the combine).
+ */
+/* Let kernels on the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * already enabled is not an error).  Call once per peer before the first moe_ep_push.
+ * (Setup helper; the reference has no counterpart.) */
+int moe_enable_peer_access(int peer_device);
+
+/* Map / unmap a peer process's device allocation (64-byte CUDA IPC handle of its base) for access
+ * from the current device.  Setup helpers; the reference has no counterpart. */
+int moe_ipc_open(const void* handle64, void** base_out);
+int moe_ipc_close(void* base);
+
+int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts, int world,
+                int rank, int combine, int d, int elem_bytes, int32_t* local_offsets, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,9 +55,10 @@ def run(args) -> list[dict]:
     strategies = ["naive_topk", "fused_select", "sinkhorn"] if args.all_strategies else (args.strategies or [args.strategy])
     results = []
     for strategy in strategies:
+        transport = getattr(args, "transport", "peer")
         layer = EPMoELayer(w_router, w1, w2, k, activation="gelu", strategy=strategy,
                            sinkhorn_iters=args.sinkhorn_iters, sinkhorn_temperature=args.sinkhorn_temperature,
-                           skew_experts=args.skew_experts, skew_bias=args.skew_bias)
+                           skew_experts=args.skew_experts, skew_bias=args.skew_bias, transport=transport)
         dist.barrier()
         for _ in range(args.warmup):
             layer(x, overlap=True)
@@ -70,16 +71,31 @@ def run(args) -> list[dict]:
             out = {}
             acc["route"] += _event_us(lambda: out.update(o=layer.route(x)))
             o = out["o"]
-            counts_all, counts_host = layer.exchange_counts(o["counts"])
-            pl = layer.plan(o, counts_all, counts_host, 1)
-            y_packed = pl["y_packed"]
+            if transport == "peer":
+                pr = layer._peer
+                counts_all = torch.empty((world, e), dtype=torch.int32, device=dev)
+                dist.all_gather_into_tensor(counts_all, o["counts"])
+                y_packed = pr["y_home"]
 
-            def comm():
-                layer.dispatch(pl, 0)
-                layer.give_back(pl, 0)
+                def comm():
+                    layer._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
+                    layer._rank_sync()
+                    layer._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
+                    layer._rank_sync()
 
-            def comp():
-                layer.compute(pl, 0)
+                def comp():
+                    layer._ffn(pr["inbox"], pr["offsets"], pr["yb"])
+            else:
+                counts_all, counts_host = layer.exchange_counts(o["counts"])
+                pl = layer.plan(o, counts_all, counts_host, 1)
+                y_packed = pl["y_packed"]
+
+                def comm():
+                    layer.dispatch(pl, 0)
+                    layer.give_back(pl, 0)
+
+                def comp():
+                    layer.compute(pl, 0)
 
             dist.barrier()
             acc["comm"] += _event_us(comm)
@@ -94,7 +110,8 @@ def run(args) -> list[dict]:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         t_route, t_comm, t_comp, t_combine, t_seq, t_ovl = [float(v) for v in vals.tolist()]
 
-        counts = layer.last["counts_all"].sum(dim=0).to(torch.float32)  # aggregated over ranks
+        counts_rk = layer.last["counts_all"] if "counts_all" in layer.last else layer.last["counts_dev"].cpu()
+        counts = counts_rk.sum(dim=0).to(torch.float32)  # aggregated over ranks
         mean = float(counts.mean())
         results.append(dict(
             strategy=strategy, world=world, tokens_per_rank=t, d_model=d, hidden=h, experts=e, top_k=k,
@@ -104,7 +121,8 @@ def run(args) -> list[dict]:
             eta_overlap=(t_route + t_comm + t_comp + t_combine) / max(t_ovl, 1e-6),
             load_max_over_mean=float(counts.max() / (mean + 1e-9)),
             load_cv=float(counts.std(unbiased=False) / (mean + 1e-9)),
-            rows_received_rank0=int(sum(sum(r_) for r_ in layer.last["plan"]["rows"])) if rank == 0 else None,
+            transport=transport,
+            rows_received_rank0=int(counts_rk[:, :el].sum()) if rank == 0 else None,
             tokens_per_s=world * t / (t_ovl * 1e-6),
         ))
     return results
@@ -127,6 +145,8 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--skew_experts", type=int, default=0)
     p.add_argument("--skew_bias", type=float, default=0.0)
+    p.add_argument("--transport", type=str, default="peer", choices=["peer", "nccl"],
+                   help="peer: device-initiated stores into the owner's inbox over NVLink; nccl: grouped send/recv")
     p.add_argument("--json", type=str, default=None, help="also write the results to this file (rank 0)")
     args = p.parse_args()
 

@@ -8,6 +8,8 @@
 // It replaces the argsort / index_select / bincount bucketing of received rows in
 // bench_2gpu_pcie.py:130-171.  Segment lengths come from the all-gathered per-rank expert counts;
 // every CTA recomputes the few prefix sums it needs (world * local_experts <= 1024 values).
+#include <cstring>
+
 #include "common.cuh"
 
 namespace moe {
@@ -95,4 +97,168 @@ extern "C" int moe_ep_rebucket(const void* src, void* dst, const int32_t* counts
       static_cast<const char*>(src), static_cast<char*>(dst), counts_all, experts, world, rank, skip_src,
       backward ? 1 : 0, (size_t)d * elem_bytes, first_local_expert, num_local_experts, local_offsets);
   return check_launch("ep_rebucket_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Device-initiated dispatch / combine over peer memory (NVLink): no staging, no re-bucketing.
+//
+// Every rank holds the all-gathered counts, so it can compute where each of its expert segments
+// belongs in the OWNER's expert-major inbox and stores the rows there directly with plain 128-bit
+// peer stores (`push`); after the expert FFN the owner stores every result row straight into the
+// packed slot of the rank it came from (`push back`).  The ranks synchronise between the phases
+// on the host side of the stream (a tiny NCCL collective): the kernels themselves never wait on a
+// peer.  No multicast, no TMA on peer memory.
+namespace moe {
+namespace {
+
+// dir 0 (dispatch): segment = (dest rank p, local expert e of p): rows packed[off_me[pE+e] ..] of this
+//   rank -> inbox of p at row B_p(me, e).
+// dir 1 (combine):  segment = (source rank s, local expert e of me): rows yb[B_me(s, e) ..] of this
+//   rank -> y_home of s at row off_s[meE + e].
+// off_r[g] = rows of rank r routed to experts < g; B_p(s, e) = rows in p's inbox before (s, e) in
+// expert-major order.
+__global__ void __launch_bounds__(kThreads)
+ep_push_kernel(const char* __restrict__ local, char* const* __restrict__ peer_bufs,
+               const int32_t* __restrict__ counts_all, int experts, int world, int rank, int dir,
+               size_t row_bytes, int32_t* __restrict__ local_offsets) {
+  __shared__ long long s_from, s_to;
+  __shared__ int s_len;
+  const int el = experts / world;
+  const int peer = blockIdx.x / el;  // dest rank (dispatch) or source rank (combine)
+  const int e = blockIdx.x % el;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const int owner = dir == 0 ? peer : rank;    // whose inbox the expert-major offset refers to
+    const int sender = dir == 0 ? rank : peer;   // whose packed order the packed offset refers to
+    const int ge = owner * el + e;               // global expert of this segment
+    // packed offset of (sender, ge): rows of `sender` routed to experts < ge
+    int off = 0;
+    for (int g = lane; g < ge; g += 32) off += counts_all[(size_t)sender * experts + g];
+    // expert-major offset of (sender, e) in owner's inbox
+    int b = 0, total = 0;
+    for (int i = lane; i < world * el; i += 32) {
+      const int ss = i / el, ee = i % el;
+      const int l = counts_all[(size_t)ss * experts + owner * el + ee];
+      if (ee < e || (ee == e && ss < sender)) b += l;
+      total += l;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      off += __shfl_xor_sync(0xffffffffu, off, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+      total += __shfl_xor_sync(0xffffffffu, total, o);
+    }
+    if (lane == 0) {
+      s_len = counts_all[(size_t)sender * experts + ge];
+      s_from = (long long)(dir == 0 ? off : b);
+      s_to = (long long)(dir == 0 ? b : off);
+    }
+    // the owner's own expert-major offsets, for its grouped GEMM (dispatch only, one CTA per expert)
+    if (dir == 0 && local_offsets != nullptr && peer == rank && blockIdx.y == 0) {
+      int first = 0, tot_mine = 0;  // rows before expert e / all rows in MY inbox
+      for (int i = lane; i < world * el; i += 32) {
+        const int ss = i / el, ee = i % el;
+        const int l = counts_all[(size_t)ss * experts + rank * el + ee];
+        if (ee < e) first += l;
+        tot_mine += l;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        first += __shfl_xor_sync(0xffffffffu, first, o);
+        tot_mine += __shfl_xor_sync(0xffffffffu, tot_mine, o);
+      }
+      if (lane == 0) {
+        local_offsets[e] = first;
+        if (e == el - 1) local_offsets[el] = tot_mine;
+      }
+    }
+  }
+  __syncthreads();
+  const size_t bytes = (size_t)s_len * row_bytes;
+  if (bytes == 0) return;
+  const char* src = local + (size_t)s_from * row_bytes;
+  char* dst = peer_bufs[peer] + (size_t)s_to * row_bytes;
+  const size_t chunk = ((bytes / gridDim.y + 15) / 16 + 1) * 16;
+  const size_t lo = (size_t)blockIdx.y * chunk;
+  const size_t hi = lo + chunk < bytes ? lo + chunk : bytes;
+  if (lo >= hi) return;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src + lo);
+  uint4* d4 = reinterpret_cast<uint4*>(dst + lo);
+  const size_t n = (hi - lo) / 16;
+  size_t i = threadIdx.x;
+  for (; i + 3 * kThreads < n; i += 4 * kThreads) {
+    const uint4 r0 = __ldg(s4 + i), r1 = __ldg(s4 + i + kThreads), r2 = __ldg(s4 + i + 2 * kThreads),
+                r3 = __ldg(s4 + i + 3 * kThreads);
+    d4[i] = r0; d4[i + kThreads] = r1; d4[i + 2 * kThreads] = r2; d4[i + 3 * kThreads] = r3;
+  }
+  for (; i < n; i += kThreads) d4[i] = __ldg(s4 + i);
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts,
+                           int world, int rank, int combine, int d, int elem_bytes, int32_t* local_offsets,
+                           void* stream) {
+  using namespace moe;
+  if (experts <= 0 || world <= 0 || experts % world != 0)
+    return fail(MOE_ERR_ARG, "experts must be divisible by world_size");
+  if (rank < 0 || rank >= world) return fail(MOE_ERR_ARG, "moe_ep_push: bad rank");
+  if (d <= 0 || (elem_bytes != 2 && elem_bytes != 4) || ((size_t)d * elem_bytes) % 16 != 0)
+    return fail(MOE_ERR_ARG, "moe_ep_push: rows must be a multiple of 16 bytes");
+  if (!local || !peer_bufs || !counts_all) return fail(MOE_ERR_ARG, "moe_ep_push: null pointer");
+  dim3 grid(experts, 8, 1);  // world * (experts / world) segments, 8 CTAs each
+  ep_push_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const char*>(local), reinterpret_cast<char* const*>(peer_bufs), counts_all, experts, world, rank,
+      combine ? 1 : 0, (size_t)d * elem_bytes, local_offsets);
+  return check_launch("ep_push_kernel");
+}
+
+extern "C" int moe_enable_peer_access(int peer_device) {
+  using namespace moe;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_enable_peer_access: %s", cudaGetErrorString(e));
+  if (peer_device == dev) return MOE_OK;
+  int can = 0;
+  e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+  if (e != cudaSuccess || !can)
+    return fail(MOE_ERR_UNSUPPORTED, "moe_enable_peer_access: device %d cannot access device %d", dev, peer_device);
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return MOE_OK;
+  }
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_enable_peer_access: %s", cudaGetErrorString(e));
+  return MOE_OK;
+}
+
+// Map a peer process's device allocation into this process for access from the CURRENT device.
+// `handle64` is the 64-byte cudaIpcMemHandle_t of the allocation's base (as exported by the owner);
+// the handle is opened with the calling rank's own device current, which is what makes the mapping
+// usable by kernels on this device (lazy peer access).  Setup helper, not on the data path.
+extern "C" int moe_ipc_open(const void* handle64, void** base_out) {
+  using namespace moe;
+  if (!handle64 || !base_out) return fail(MOE_ERR_ARG, "moe_ipc_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* base = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(MOE_ERR_LAUNCH, "moe_ipc_open: %s", cudaGetErrorString(e));
+  }
+  *base_out = base;
+  return MOE_OK;
+}
+
+extern "C" int moe_ipc_close(void* base) {
+  using namespace moe;
+  if (!base) return MOE_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(base);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(MOE_ERR_LAUNCH, "moe_ipc_close: %s", cudaGetErrorString(e));
+  }
+  return MOE_OK;
 }

@@ -84,7 +84,7 @@ class EPMoELayer:
 
     def __init__(self, w_router, w1_local, w2_local, top_k: int = 2, *, activation: str = "gelu",
                  strategy: str = "fused_select", sinkhorn_iters: int = 10, sinkhorn_temperature: float = 1.0,
-                 skew_experts: int = 0, skew_bias: float = 0.0, group=None):
+                 skew_experts: int = 0, skew_bias: float = 0.0, group=None, transport: str = "peer"):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -102,6 +102,13 @@ class EPMoELayer:
         self.strategy = strategy
         self.sinkhorn_iters, self.sinkhorn_temperature = sinkhorn_iters, sinkhorn_temperature
         self.skew_experts, self.skew_bias = skew_experts, skew_bias
+        if transport not in ("peer", "nccl"):
+            raise ValueError("transport must be 'peer' or 'nccl'")
+        # "peer": device-initiated dispatch/combine, rows stored straight into the owner's expert-major
+        # inbox over NVLink (CUDA IPC mappings), no host synchronisation in the layer.
+        # "nccl": grouped NCCL send/recv plus re-bucketing on the owner.
+        self.transport = transport
+        self._peer = None
         self.comm_stream = torch.cuda.Stream()
         # Expert groups pipelined against the exchanges, and SMs the persistent GEMM leaves to the
         # exchange kernels while it runs.  Measured on 2 B200s (T=4096/rank, d=4096, h=8192, E=64):
@@ -205,9 +212,97 @@ class EPMoELayer:
             pl["back"][c][r].copy_(ret[r])
         self._exchange(ret, pl["back"][c])
 
+    # ---- device-initiated transport ------------------------------------------------------------
+    def _setup_peer(self, rows_home: int, d: int, dtype, device):
+        """Allocate this rank's inbox / result buffers and map every peer's into this process.
+        inbox: worst case all W * rows_home routes of the job land on this rank."""
+        import ctypes
+
+        w = self.world
+        sizes = [None] * w
+        dist.all_gather_object(sizes, int(rows_home), group=self.group)
+        cap = w * max(sizes)  # ranks may hold different numbers of tokens
+        inbox = torch.empty((cap, d), dtype=dtype, device=device)
+        y_home = torch.empty((rows_home, d), dtype=dtype, device=device)
+
+        def export(t):
+            # (device, ipc handle of the allocation's base, size, offset of the storage in it, ...)
+            meta = t.untyped_storage()._share_cuda_()
+            handle = bytes(meta[1])
+            if len(handle) == 66:  # torch prefixes a version byte and a kind byte ('c' = cudaMalloc)
+                if handle[1:2] != b"c":
+                    raise RuntimeError("peer transport needs cudaMalloc-backed tensors (no expandable segments)")
+                handle = handle[2:]
+            if len(handle) != 64:
+                raise RuntimeError(f"unexpected CUDA IPC handle size {len(handle)}")
+            return handle, int(meta[3]) + t.storage_offset() * t.element_size()
+
+        gathered = [None] * w
+        dist.all_gather_object(gathered, (export(inbox), export(y_home)), group=self.group)
+        opened = {}  # one mapping per distinct allocation
+
+        def map_peer(handle, offset):
+            if handle not in opened:
+                base = ctypes.c_void_p()
+                with torch.cuda.device(device):  # opened with THIS rank's device current
+                    check(lib.moe_ipc_open(handle, ctypes.byref(base)))
+                opened[handle] = base.value
+            return opened[handle] + offset
+
+        in_ptrs, home_ptrs = [], []
+        for p_ in range(w):
+            if p_ == self.rank:
+                in_ptrs.append(inbox.data_ptr())
+                home_ptrs.append(y_home.data_ptr())
+            else:
+                (h_i, o_i), (h_h, o_h) = gathered[p_]
+                in_ptrs.append(map_peer(h_i, o_i))
+                home_ptrs.append(map_peer(h_h, o_h))
+        self._peer = dict(
+            rows_home=rows_home, d=d, cap=cap, inbox=inbox, y_home=y_home, mappings=opened,
+            inbox_ptrs=torch.tensor(in_ptrs, dtype=torch.int64, device=device),
+            home_ptrs=torch.tensor(home_ptrs, dtype=torch.int64, device=device),
+            yb=torch.empty((cap, d), dtype=dtype, device=device),
+            offsets=torch.zeros(self.el + 1, dtype=torch.int32, device=device),
+            flag=torch.zeros(1, dtype=torch.int32, device=device),
+        )
+        dist.barrier(group=self.group)
+
+    def _push(self, local, ptrs, counts_all, combine, local_offsets):
+        check(lib.moe_ep_push(local.data_ptr(), ptrs.data_ptr(), counts_all.data_ptr(), self.e, self.world, self.rank,
+                              1 if combine else 0, local.size(1), local.element_size(),
+                              local_offsets.data_ptr() if local_offsets is not None else None,
+                              torch.cuda.current_stream().cuda_stream))
+
+    def _rank_sync(self):
+        """Order the phases across ranks on the stream: a one-element all-reduce (no host wait)."""
+        dist.all_reduce(self._peer["flag"], group=self.group)
+
+    def forward_peer(self, x: torch.Tensor) -> torch.Tensor:
+        o = self.route(x)
+        packed = o["packed"]
+        rows_home, d = packed.shape
+        if self._peer is None or self._peer["rows_home"] != rows_home or self._peer["d"] != d:
+            self._setup_peer(rows_home, d, packed.dtype, packed.device)
+        pr = self._peer
+        counts_all = torch.empty((self.world, self.e), dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(counts_all, o["counts"], group=self.group)
+        # every rank has left the previous call's combine before anybody overwrites an inbox: the
+        # all-gather above is that barrier (it completes only when every rank has reached it)
+        self._push(packed, pr["inbox_ptrs"], counts_all, False, pr["offsets"])
+        self._rank_sync()  # all rows have arrived in every inbox
+        self._ffn(pr["inbox"], pr["offsets"], pr["yb"])
+        self._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
+        self._rank_sync()  # all results are back in their home slots
+        out = ops.combine(pr["y_home"], o["gates"], o["route_row"], self.k)
+        self.last = dict(counts_dev=counts_all, route=o)
+        return out
+
     def forward(self, x: torch.Tensor, *, overlap: bool = True, chunks: Optional[int] = None) -> torch.Tensor:
         if not x.is_cuda:
             raise RuntimeError("inputs must be CUDA")
+        if self.transport == "peer":
+            return self.forward_peer(x)
         main = torch.cuda.current_stream()
         comm = self.comm_stream if overlap else main
         if chunks is None:

@@ -61,6 +61,48 @@ def _free_port():
     return p
 
 
+@pytest.mark.parametrize("world,e,d", [(4, 16, 64), (2, 8, 40), (8, 64, 128), (1, 4, 8)])
+def test_push_kernel_emulated_ranks(world, e, d):
+    """Device-initiated dispatch and combine with all ranks emulated on one GPU: every "rank" pushes
+    its packed rows into the owners' inboxes, then every owner pushes its inbox back; rows must land
+    expert-major in the inbox and return to the exact packed slot they came from."""
+    _need_cuda()
+    from moe_routers_b200 import _lib
+
+    el = e // world
+    rng = np.random.default_rng(world + e)
+    counts_all = rng.integers(0, 30, size=(world, e)).astype(np.int32)
+    if world > 1:
+        counts_all[rng.integers(0, world), rng.integers(0, e)] = 0
+    c_t = torch.from_numpy(counts_all).cuda()
+    packed = [torch.from_numpy(rng.standard_normal((int(counts_all[r].sum()) + 1, d)).astype(np.float16)).cuda()
+              for r in range(world)]
+    cap = int(counts_all.sum()) + 1
+    inbox = [torch.zeros((cap, d), dtype=torch.float16, device="cuda") for _ in range(world)]
+    home = [torch.zeros_like(packed[r]) for r in range(world)]
+    in_ptrs = torch.tensor([t.data_ptr() for t in inbox], dtype=torch.int64, device="cuda")
+    home_ptrs = torch.tensor([t.data_ptr() for t in home], dtype=torch.int64, device="cuda")
+    offs = [torch.full((el + 1,), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    st = torch.cuda.current_stream().cuda_stream
+    for r in range(world):
+        _lib.check(_lib.lib.moe_ep_push(packed[r].data_ptr(), in_ptrs.data_ptr(), c_t.data_ptr(), e, world, r, 0, d, 2,
+                                        offs[r].data_ptr(), st))
+    off_r = np.concatenate([np.zeros((world, 1), np.int64), np.cumsum(counts_all, axis=1)], axis=1)
+    for p_ in range(world):
+        segs = [packed[s_].cpu().numpy()[off_r[s_, p_ * el + ee]:off_r[s_, p_ * el + ee + 1]]
+                for ee in range(el) for s_ in range(world)]
+        expect = np.concatenate(segs + [np.zeros((0, d), np.float16)])
+        np.testing.assert_array_equal(inbox[p_].cpu().numpy()[:len(expect)], expect)
+        exp_off = np.concatenate([[0], np.cumsum(counts_all[:, p_ * el:(p_ + 1) * el].sum(axis=0))]).astype(np.int32)
+        np.testing.assert_array_equal(offs[p_].cpu().numpy(), exp_off)
+    for r in range(world):
+        _lib.check(_lib.lib.moe_ep_push(inbox[r].data_ptr(), home_ptrs.data_ptr(), c_t.data_ptr(), e, world, r, 1, d, 2,
+                                        None, st))
+    for r in range(world):
+        n = int(counts_all[r].sum())
+        np.testing.assert_array_equal(home[r].cpu().numpy()[:n], packed[r].cpu().numpy()[:n])
+
+
 def _ep_worker(rank, world, port, strategy, q):
     try:
         import torch.distributed as dist
@@ -78,10 +120,12 @@ def _ep_worker(rank, world, port, strategy, q):
         w2 = (torch.randn(e, d, h, generator=gw) / h ** 0.5).half()
         gx = torch.Generator().manual_seed(10 + rank)
         x = torch.randn(t, d, generator=gx).half()
-        layer = EPMoELayer(w_router.cuda(), w1[rank * el:(rank + 1) * el].cuda().contiguous(),
-                           w2[rank * el:(rank + 1) * el].cuda().contiguous(), k, activation="gelu",
-                           strategy=strategy, skew_experts=4, skew_bias=2.0)
-        for overlap in (True, False):
+        layers = {tr: EPMoELayer(w_router.cuda(), w1[rank * el:(rank + 1) * el].cuda().contiguous(),
+                                 w2[rank * el:(rank + 1) * el].cuda().contiguous(), k, activation="gelu",
+                                 strategy=strategy, skew_experts=4, skew_bias=2.0, transport=tr)
+                  for tr in ("peer", "nccl")}
+        for tr, overlap in (("peer", True), ("peer", True), ("nccl", True), ("nccl", False)):
+            layer = layers[tr]
             out = layer(x.cuda(), overlap=overlap)
             torch.cuda.synchronize()
             o = layer.last["route"]
