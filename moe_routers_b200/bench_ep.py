@@ -125,6 +125,7 @@ def run(args) -> list[dict]:
             rows_received_rank0=int(counts_rk[:, :el].sum()) if rank == 0 else None,
             tokens_per_s=world * t / (t_ovl * 1e-6),
         ))
+        layer.close()
     return results
 
 

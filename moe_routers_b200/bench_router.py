@@ -4,6 +4,9 @@ printed table (:596-601).
 
     python -m moe_routers_b200.bench_router --all_strategies --skew_experts 8 --skew_bias 2.0
 
+`--perm_sweep` mirrors the reference's permutation sweep (:284-388): pack latency against batch
+size with the DRAM-limit model, written as CSV (no plot).
+
 Stages are timed one by one with CUDA events and a device synchronise, like the reference
 (`_cuda_time`, :47-54); because that protocol hides what fusion saves, the fused single-call
 route time is printed next to it (`T_fused`).  There is no CPU path here: `--device cpu` is refused
@@ -29,6 +32,52 @@ def _cuda_time(fn) -> float:
     return float(start.elapsed_time(end))
 
 
+def _torch_pack(x, topk_idx):
+    """The reference's sorted pack (bench_router.py:57-78) in torch ops, without the gate multiply:
+    the comparison leg of the permutation sweep."""
+    s_, k_ = topk_idx.shape
+    token_ids = torch.arange(s_, device=x.device, dtype=torch.int64).unsqueeze(1).expand(s_, k_).reshape(-1)
+    sort_idx = torch.argsort(topk_idx.reshape(-1).to(torch.int64))
+    return x.index_select(0, token_ids).index_select(0, sort_idx)
+
+
+def run_perm_sweep(args) -> None:
+    """Permutation latency against batch size with the DRAM-limit model of bench_router.py:284-388:
+    random uniform routes, t_theory = 2 * R * d * elem / peak (the reference's "ideal one pass";
+    the compulsory traffic (1 + k) * T * d * elem is reported beside it)."""
+    import csv
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    bw = float(args.peak_bw_gbs) if args.peak_bw_gbs is not None else 6548.8
+    e, k, d = args.experts, args.top_k, args.d_model
+    rows = []
+    for bsz in args.batch_sizes:
+        tokens = int(bsz) * int(args.seq_len)
+        x = torch.randn(tokens, d, device=dev).half()
+        idx = torch.randint(0, e, (tokens, k), device=dev, dtype=torch.int32)
+        for _ in range(args.warmup):
+            ops.pack(x, idx, e)
+            _torch_pack(x, idx)
+        t_ours = sum(_cuda_time(lambda: ops.pack(x, idx, e)) for _ in range(args.iters)) / max(args.iters, 1)
+        t_torch = sum(_cuda_time(lambda: _torch_pack(x, idx)) for _ in range(args.iters)) / max(args.iters, 1)
+        routes = tokens * k
+        ideal = 2.0 * routes * d * 2
+        rows.append(dict(batch_size=int(bsz), seq_len=int(args.seq_len), tokens=tokens, experts=e, top_k=k, d_model=d,
+                         dtype="float16", t_perm_naive_ms=t_torch, t_perm_sorted_ms=t_ours,
+                         t_theory_ms=ideal / (bw * 1e9) * 1e3, peak_bw_gbs=bw,
+                         sorted_achieved_bw_gbs=ideal / (t_ours * 1e-3) / 1e9,
+                         compulsory_bytes=(1 + k) * tokens * d * 2))
+    with open(args.csv_out, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=list(rows[0].keys()))
+        w.writeheader()
+        w.writerows(rows)
+    print("perm_sweep: wrote CSV:", args.csv_out)
+    for r in rows:
+        print(f"B={r['batch_size']:<4d} tokens={r['tokens']:<6d} torch {r['t_perm_naive_ms'] * 1e3:8.1f} us  "
+              f"ours {r['t_perm_sorted_ms'] * 1e3:8.1f} us  theory {r['t_theory_ms'] * 1e3:7.1f} us")
+
+
 def main() -> None:
     p = argparse.ArgumentParser()
     p.add_argument("--device", type=str, default="cuda")
@@ -46,9 +95,18 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--skew_experts", type=int, default=0)
     p.add_argument("--skew_bias", type=float, default=0.0)
+    p.add_argument("--perm_sweep", action="store_true",
+                   help="Sweep batch size and measure the pack (permutation) latency against the DRAM limit.")
+    p.add_argument("--batch_sizes", type=int, nargs="+", default=[1, 2, 4, 8, 16, 32, 64])
+    p.add_argument("--seq_len", type=int, default=128, help="Used with --perm_sweep: tokens = batch_size * seq_len")
+    p.add_argument("--csv_out", type=str, default="perm_efficiency.csv")
+    p.add_argument("--peak_bw_gbs", type=float, default=None)
     args = p.parse_args()
     if torch.device(args.device).type != "cuda":
         raise RuntimeError("inputs must be CUDA: this library has no CPU path")
+    if args.perm_sweep:
+        run_perm_sweep(args)
+        return
 
     torch.manual_seed(0)
     dev = torch.device("cuda")

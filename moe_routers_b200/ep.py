@@ -238,7 +238,8 @@ class EPMoELayer:
             return handle, int(meta[3]) + t.storage_offset() * t.element_size()
 
         gathered = [None] * w
-        dist.all_gather_object(gathered, (export(inbox), export(y_home)), group=self.group)
+        if w > 1:
+            dist.all_gather_object(gathered, (export(inbox), export(y_home)), group=self.group)
         opened = {}  # one mapping per distinct allocation
 
         def map_peer(handle, offset):
@@ -267,6 +268,14 @@ class EPMoELayer:
             flag=torch.zeros(1, dtype=torch.int32, device=device),
         )
         dist.barrier(group=self.group)
+
+    def close(self):
+        """Unmap the peers' buffers (call before the process group goes away)."""
+        if self._peer is not None:
+            torch.cuda.synchronize()
+            for base in self._peer["mappings"].values():
+                check(lib.moe_ipc_close(base))
+            self._peer = None
 
     def _push(self, local, ptrs, counts_all, combine, local_offsets):
         check(lib.moe_ep_push(local.data_ptr(), ptrs.data_ptr(), counts_all.data_ptr(), self.e, self.world, self.rank,

@@ -137,6 +137,8 @@ def _ep_worker(rank, world, port, strategy, q):
             # layer outputs: 2e-2 relative to the output scale (fp16)
             np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2 * scale)
         dist.barrier()
+        for layer in layers.values():
+            layer.close()
         dist.destroy_process_group()
         q.put((rank, "ok"))
     except Exception as exc:  # pragma: no cover
