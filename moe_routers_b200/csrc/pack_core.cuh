@@ -28,6 +28,14 @@ __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ id
                                                   int32_t* s_total, int32_t* s_dst, int32_t* status) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  // warp 0 ranks the routes later; it fetches their expert ids now so that the loads overlap the
+  // histogram pass (at most 8 chunks of 32 routes per tile)
+  int my_e[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int r = c * 32 + lane;
+    my_e[c] = (warp == 0 && r < tile_routes) ? __ldcg(idx + (size_t)t0 * top_k + r) : -1;
+  }
   if (tile_base != nullptr) {
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
       s_base[e] = tile_base[(size_t)tile * experts + e];
@@ -36,29 +44,53 @@ __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ id
   } else {
     for (int e = threadIdx.x; e < experts; e += blockDim.x) { s_base[e] = 0; s_total[e] = 0; }
     __syncthreads();
-    const int parts = max(1, (int)blockDim.x / experts);
-    for (int cell = threadIdx.x; cell < experts * parts; cell += blockDim.x) {
-      const int e = cell % experts;
-      const int pt = cell / experts;
-      int before = 0, total = 0;
-      int t = pt;
-      for (; t + 7 * parts < num_tiles; t += 8 * parts) {
-        int h[8];
+    if ((experts & 3) == 0 && experts / 4 <= (int)blockDim.x) {
+      // 128-bit loads: a thread owns 4 consecutive experts and every `parts`-th tile, so that all of
+      // its loads (num_tiles / parts of them) are in flight together - one L2 round trip, not four
+      const int vecs = experts / 4;
+      const int parts = (int)blockDim.x / vecs;
+      const int v = threadIdx.x % vecs;
+      const int pt = threadIdx.x / vecs;
+      if (pt < parts) {
+        int before[4] = {0, 0, 0, 0}, total[4] = {0, 0, 0, 0};
+        const int4* th4 = reinterpret_cast<const int4*>(tile_hist);
+        int t = pt;
+        for (; t + 7 * parts < num_tiles; t += 8 * parts) {
+          int4 h[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) h[u] = __ldcg(tile_hist + (size_t)(t + u * parts) * experts + e);
+          for (int u = 0; u < 8; ++u) h[u] = __ldcg(th4 + (size_t)(t + u * parts) * vecs + v);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          total += h[u];
-          if (t + u * parts < tile) before += h[u];
+          for (int u = 0; u < 8; ++u) {
+            const bool early = t + u * parts < tile;
+            total[0] += h[u].x; total[1] += h[u].y; total[2] += h[u].z; total[3] += h[u].w;
+            if (early) { before[0] += h[u].x; before[1] += h[u].y; before[2] += h[u].z; before[3] += h[u].w; }
+          }
+        }
+        for (; t < num_tiles; t += parts) {
+          const int4 h = __ldcg(th4 + (size_t)t * vecs + v);
+          total[0] += h.x; total[1] += h.y; total[2] += h.z; total[3] += h.w;
+          if (t < tile) { before[0] += h.x; before[1] += h.y; before[2] += h.z; before[3] += h.w; }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          atomicAdd(&s_base[4 * v + i], before[i]);
+          atomicAdd(&s_total[4 * v + i], total[i]);
         }
       }
-      for (; t < num_tiles; t += parts) {
-        const int h = __ldcg(tile_hist + (size_t)t * experts + e);
-        total += h;
-        if (t < tile) before += h;
+    } else {
+      const int parts = max(1, (int)blockDim.x / experts);
+      for (int cell = threadIdx.x; cell < experts * parts; cell += blockDim.x) {
+        const int e = cell % experts;
+        const int pt = cell / experts;
+        int before = 0, total = 0;
+        for (int t = pt; t < num_tiles; t += parts) {
+          const int h = __ldcg(tile_hist + (size_t)t * experts + e);
+          total += h;
+          if (t < tile) before += h;
+        }
+        atomicAdd(&s_base[e], before);
+        atomicAdd(&s_total[e], total);
       }
-      atomicAdd(&s_base[e], before);
-      atomicAdd(&s_total[e], total);
     }
   }
   __syncthreads();
@@ -87,10 +119,13 @@ __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ id
     if (publish && lane == 0) offsets[experts] = carry;
     __syncwarp();
 
-    for (int c = 0; c < tile_routes; c += 32) {
+#pragma unroll
+    for (int ci = 0; ci < 8; ++ci) {
+      const int c = ci * 32;
+      if (c >= tile_routes) break;
       const int r = c + lane;
       const bool in_tile = r < tile_routes;
-      const int e = in_tile ? __ldcg(idx + (size_t)t0 * top_k + r) : -1;
+      const int e = my_e[ci];
       const bool valid = in_tile && (unsigned)e < (unsigned)experts;
       if (in_tile && !valid) record_error(status, kErrBadIndex);
       const unsigned key = valid ? (unsigned)e : (0x40000000u + lane);

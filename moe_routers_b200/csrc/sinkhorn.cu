@@ -97,7 +97,6 @@ sinkhorn_kernel(const SParams p) {
   const int E = p.experts;
   const int R = p.rows_per_cta;
   const int nthreads = (int)blockDim.x;
-  const int nwarps = nthreads >> 5;
   const int nblk = (int)gridDim.x;
   const int cw = min(E, nthreads);       // columns handled side by side
   const int groups = nthreads / cw;      // row groups working on the same column
