@@ -60,7 +60,8 @@ def test_router_gemm_select(ops, t, d, e, k, skew_n, skew_b):
 
 @pytest.mark.parametrize("t,d,e,k,skew_n,skew_b", SHAPES[:5] + [(0, 64, 64, 2, 0, 0.0), (4736, 1024, 64, 2, 8, 2.0),
                                                     (5000, 1024, 64, 2, 0, 0.0), (31, 2048, 64, 8, 0, 0.0),
-                                                    (1000, 8192, 32, 2, 0, 0.0), (513, 1024, 256, 3, 0, 0.0)])
+                                                    (1000, 8192, 32, 2, 0, 0.0), (513, 1024, 256, 3, 0, 0.0),
+                                                    (9000, 256, 64, 2, 8, 2.0)])
 def test_route_fused(ops, t, d, e, k, skew_n, skew_b):
     x, w = _inputs(t, d, e, 5 + t + d + e)
     o = ops.route_fused(x.cuda(), w.cuda(), k, skew_experts=skew_n, skew_bias=skew_b, return_logits=t > 0)

@@ -87,6 +87,9 @@ def _random_routes(t, e, k, seed, skew=False):
     (127, 72, 64, 2, torch.float16, True), (129, 100, 16, 4, torch.float32, False),
     (1000, 250, 64, 8, torch.bfloat16, True), (33, 3, 4, 1, torch.float16, False),
     (257, 36, 300, 3, torch.float16, False), (0, 64, 64, 2, torch.float16, False),
+    # more than 256 tiles of 32 tokens: the separate per-expert scan kernel computes the tile bases
+    (10000, 64, 64, 2, torch.float16, True), (8193, 24, 8, 4, torch.float16, False),
+    (20000, 128, 256, 1, torch.bfloat16, False),
 ])
 def test_pack_bit_exact(ops, t, d, e, k, dtype, skew):
     idx = _random_routes(t, e, k, 7 + t + d, skew)
