@@ -95,6 +95,9 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--skew_experts", type=int, default=0)
     p.add_argument("--skew_bias", type=float, default=0.0)
+    p.add_argument("--layer", action="store_true",
+                   help="Also time the whole MoE layer per strategy (route + 2-layer GELU expert FFN + combine).")
+    p.add_argument("--hidden", type=int, default=8192, help="expert hidden size used with --layer")
     p.add_argument("--perm_sweep", action="store_true",
                    help="Sweep batch size and measure the pack (permutation) latency against the DRAM limit.")
     p.add_argument("--batch_sizes", type=int, nargs="+", default=[1, 2, 4, 8, 16, 32, 64])
@@ -140,6 +143,28 @@ def main() -> None:
         rows = [one_iter(s) for _ in range(args.iters)]
         results[s] = [sum(r[i] for r in rows) / len(rows) for i in range(5)]
 
+    layer_ms = {}
+    if args.layer:
+        from .strategies import masked_matmul_forward, moe_forward
+
+        h = args.hidden
+        w1 = (torch.randn(e, h, args.d_model, device=dev) / args.d_model ** 0.5).half()
+        w2 = (torch.randn(e, args.d_model, h, device=dev) / h ** 0.5).half()
+
+        def layer_once(strategy):
+            r = route(strategy, x, w, k, sinkhorn_iters=args.sinkhorn_iters,
+                      sinkhorn_temperature=args.sinkhorn_temperature, **kw)
+            if strategy == "masked_matmul":
+                return masked_matmul_forward(x, r, w1, w2, k)
+            return moe_forward(r, w1, w2, k)
+
+        for s in strategies:
+            if s == "masked_matmul" and e > 8:
+                continue  # Strategy A is defined for small expert counts (benchmark configuration 3: E=8)
+            for _ in range(args.warmup):
+                layer_once(s)
+            layer_ms[s] = sum(_cuda_time(lambda: layer_once(s)) for _ in range(args.iters)) / max(args.iters, 1)
+
     print("strategies:", strategies)
     print("device:", dev, "dtype: torch.float16")
     print("T(tokens):", args.tokens, "d_model:", args.d_model, "E:", e, "k:", k)
@@ -150,8 +175,13 @@ def main() -> None:
     for s in strategies:
         r = results[s]
         print(f"{s:<14} {r[0]:10.3f} {r[1]:10.3f} {r[2]:10.3f} {r[3]:10.3f} {r[4]:10.3f}")
-    print(json.dumps({s: dict(zip(("t_logit_ms", "t_select_ms", "t_pack_ms", "t_route_ms", "t_fused_ms"), results[s]))
-                      for s in strategies}))
+    if layer_ms:
+        print("")
+        print(f"=== MoE layer (route + expert FFN hidden={args.hidden} + combine), ms, mean ===")
+        for s, v in layer_ms.items():
+            print(f"{s:<14} {v:10.3f}")
+    print(json.dumps({s: dict(zip(("t_logit_ms", "t_select_ms", "t_pack_ms", "t_route_ms", "t_fused_ms"), results[s]),
+                              t_layer_ms=layer_ms.get(s)) for s in strategies}))
 
 
 if __name__ == "__main__":
