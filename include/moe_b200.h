@@ -134,22 +134,22 @@ int moe_combine(const void* y, int dtype, const float* gates, const int32_t* rou
  * (bench_router.py:512-516) and fused_select_forward
  * (kernels/fused_select.cu:203-311); the logits never go to HBM unless
  * `logits_out` is given.
- *   x [tokens, d] fp16, w_router [experts, d] fp16 (both row-major, d % 8 == 0)
+ *   x [tokens, d], w_router [experts, d]: both `dtype` (MOE_F16 or MOE_BF16), row-major, d % 8 == 0
  *   skew: logits[:, :skew_experts] += skew_bias, applied after the logits are
- *         rounded to fp16 (the dtype the reference computes them in)
+ *         rounded to `dtype` (the dtype the reference computes them in)
  *   logits_out: NULL or [tokens, experts] float32 receiving the values the
  *         selection saw
  *   remaining outputs as in moe_topk_select and moe_pack.
  * Limits: experts <= 256, 1 <= top_k <= 8, top_k <= experts, d % 8 == 0.
  */
-int moe_route_fused(const void* x, const void* w_router, int tokens, int d, int experts, int top_k,
+int moe_route_fused(const void* x, const void* w_router, int dtype, int tokens, int d, int experts, int top_k,
                     int skew_experts, float skew_bias, int32_t* idx, float* gates, int32_t* counts,
                     int32_t* offsets, void* packed, int32_t* row_route, int32_t* route_row,
                     float* logits_out, void* workspace, size_t workspace_bytes, void* stream);
 
 /* The logit GEMM + select half of moe_route_fused on its own (T_logit +
  * T_select of bench_router.py:512-545 in one launch). */
-int moe_router_gemm_select(const void* x, const void* w_router, int tokens, int d, int experts,
+int moe_router_gemm_select(const void* x, const void* w_router, int dtype, int tokens, int d, int experts,
                            int top_k, int skew_experts, float skew_bias, int32_t* idx, float* gates,
                            float* logits_out, void* workspace, size_t workspace_bytes, void* stream);
 
@@ -178,12 +178,15 @@ int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, int experts, 
  * Replaces: grouped_ffn_forward (kernels/grouped_ffn.cu:53-136) and the
  * per-expert loops (bench_2gpu_pcie.py:123-171, models/decoder_moe.py:256-273,
  * fused_select.py:74-93).
- *   a [rows, K] fp16 row-major; w: `experts` matrices, stride_w elements apart,
- *   each [K,N] (MOE_W_KN) or [N,K] (MOE_W_NK); c [rows, N] fp16
+ *   a [rows, K] row-major; w: `experts` matrices, stride_w elements apart,
+ *   each [K,N] (MOE_W_KN) or [N,K] (MOE_W_NK); c [rows, N]; all 16-bit (`dtype`)
  *   (for MOE_ACT_SWIGLU the weight has 2N output features, gate then up, and
  *   c = silu(gate) * up has N columns)
  *   offsets [experts+1] int32 on the device; `rows` is the capacity of a / c
  *   row_scale: NULL or float32 [rows] multiplied into the result rows.
+ *   bias:      NULL or [experts, output features of W] in `dtype`, added before the activation
+ *              (the `+ b1[e]` / `+ b2[e]` loops of fused_select.py:74-93).
+ *   dtype:     MOE_F16 or MOE_BF16 for a, w, bias and c.
  *   sm_margin: SMs the persistent grid leaves free (0 = use all), so that a communication
  *              kernel running on another stream can make progress next to it.
  * Limits: K % 8 == 0; N % 16 == 0 for [N,K] weights, N % 64 == 0 for [K,N] weights;
@@ -191,8 +194,8 @@ int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, int experts, 
  */
 int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts,
                      int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
-                     const float* row_scale, int sm_margin, void* workspace, size_t workspace_bytes,
-                     void* stream);
+                     const float* row_scale, const void* bias, int dtype, int sm_margin, void* workspace,
+                     size_t workspace_bytes, void* stream);
 
 /*
  * Expert-parallel re-bucketing of rows received by the dispatch all-to-all.

@@ -31,15 +31,15 @@ SIGNATURES = {
     "moe_pack": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "moe_pack_static": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p]),
     "moe_combine": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _p]),
-    "moe_route_fused": (_i, [_p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
-    "moe_router_gemm_select": (_i, [_p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _sz, _p]),
+    "moe_route_fused": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "moe_router_gemm_select": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _sz, _p]),
     "moe_ep_rebucket": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p]),
     "moe_enable_peer_access": (_i, [_i]),
     "moe_ipc_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "moe_ipc_close": (_i, [_p]),
     "moe_ep_push": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]),
     "moe_sinkhorn": (_i, [_p, _i, _i, _i, _i, _i, _f, _f, _p, _p, _p, _sz, _p]),
-    "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _i, _p, _sz, _p]),
+    "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),
 }
 
 

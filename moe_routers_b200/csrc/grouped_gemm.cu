@@ -37,7 +37,9 @@ struct GParams {
   int w_kn;     // 1: weights stored [K, N] (N contiguous) -> MN-major B operand
   int act;      // MOE_ACT_*
   const float* row_scale;
-  __half* c;
+  const uint16_t* bias;  // [experts, n_w] in the data type, or null
+  int bf16;              // 0: fp16 data, 1: bf16 data
+  uint16_t* c;
   int32_t* status;
 };
 
@@ -64,15 +66,37 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[W]) {
   if constexpr (W == 32) tmem_ld32(taddr, v); else tmem_ld16(taddr, v);
 }
 
-// W accumulator columns of one row: TMEM -> registers -> activation -> fp16 -> global.
+__device__ __forceinline__ float load16(const uint16_t* p, bool bf16) {
+  return bf16 ? __bfloat162float(__ushort_as_bfloat16(*p)) : __half2float(__ushort_as_half(*p));
+}
+__device__ __forceinline__ uint32_t pack16x2(float a, float b, bool bf16) {
+  if (bf16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// W accumulator columns of one row: TMEM -> registers -> (+bias) -> activation -> 16-bit -> global.
+// bias_main / bias_up point at the bias entries of these columns (null: no bias).
 template <int W>
 __device__ __forceinline__ void epilogue_chunk(uint32_t t_main, uint32_t t_up, bool swiglu, int act, float scale,
-                                               bool valid, __half* dst_h) {
+                                               bool valid, uint16_t* dst_h, const uint16_t* bias_main,
+                                               const uint16_t* bias_up, bool bf16) {
   float v[W];
   tmem_ld<W>(t_main, v);
+  if (bias_main != nullptr) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) v[i] += load16(bias_main + i, bf16);
+  }
   if (swiglu) {
     float u[W];
     tmem_ld<W>(t_up, u);
+    if (bias_up != nullptr) {
+#pragma unroll
+      for (int i = 0; i < W; ++i) u[i] += load16(bias_up + i, bf16);
+    }
 #pragma unroll
     for (int i = 0; i < W; ++i) v[i] = silu(v[i]) * u[i];
   } else if (act == MOE_ACT_GELU) {
@@ -86,15 +110,11 @@ __device__ __forceinline__ void epilogue_chunk(uint32_t t_main, uint32_t t_up, b
     uint4* dst = reinterpret_cast<uint4*>(dst_h);
 #pragma unroll
     for (int i = 0; i < W / 8; ++i) {
-      __half2 h0 = __floats2half2_rn(v[8 * i + 0] * scale, v[8 * i + 1] * scale);
-      __half2 h1 = __floats2half2_rn(v[8 * i + 2] * scale, v[8 * i + 3] * scale);
-      __half2 h2 = __floats2half2_rn(v[8 * i + 4] * scale, v[8 * i + 5] * scale);
-      __half2 h3 = __floats2half2_rn(v[8 * i + 6] * scale, v[8 * i + 7] * scale);
       uint4 o;
-      o.x = *reinterpret_cast<uint32_t*>(&h0);
-      o.y = *reinterpret_cast<uint32_t*>(&h1);
-      o.z = *reinterpret_cast<uint32_t*>(&h2);
-      o.w = *reinterpret_cast<uint32_t*>(&h3);
+      o.x = pack16x2(v[8 * i + 0] * scale, v[8 * i + 1] * scale, bf16);
+      o.y = pack16x2(v[8 * i + 2] * scale, v[8 * i + 3] * scale, bf16);
+      o.z = pack16x2(v[8 * i + 4] * scale, v[8 * i + 5] * scale, bf16);
+      o.w = pack16x2(v[8 * i + 6] * scale, v[8 * i + 7] * scale, bf16);
       dst[i] = o;
     }
   }
@@ -211,7 +231,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(kBM, BN, 0, 0, p.w_kn);
+      const uint32_t idesc = make_idesc_f16(kBM, BN, p.bf16, 0, p.w_kn);
       uint32_t it = 0;
       int local = 0;
       bool ok = true;
@@ -257,13 +277,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
       const float scale = (valid && p.row_scale != nullptr) ? p.row_scale[grow] : 1.f;
-      __half* crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
+      uint16_t* crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
+      // bias of expert e: main columns at nt*out_bn, SwiGLU up columns n_out further
+      const int n_w = swiglu ? 2 * p.n_out : p.n_out;
+      const uint16_t* brow = p.bias ? p.bias + (size_t)e * n_w + (size_t)nt * out_bn : nullptr;
       if (out_bn % 32 == 0) {
         for (int c0 = 0; c0 < out_bn; c0 += 32)
-          epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0);
+          epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0,
+                             brow ? brow + c0 : nullptr, (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
       } else {
         for (int c0 = 0; c0 < out_bn; c0 += 16)
-          epilogue_chunk<16>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0);
+          epilogue_chunk<16>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0,
+                             brow ? brow + c0 : nullptr, (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
       }
       tc_fence_before();
       mbar_arrive(tempty0 + 8 * ab);  // this thread is done reading the accumulator
@@ -283,8 +308,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts, int rows,
                                 int K, int N, int w_layout, int64_t stride_w, int activation,
-                                const float* row_scale, int sm_margin, void* workspace, size_t workspace_bytes,
-                                void* stream) {
+                                const float* row_scale, const void* bias, int dtype, int sm_margin,
+                                void* workspace, size_t workspace_bytes, void* stream) {
   using namespace moe;
   if (experts <= 0 || rows < 0 || K <= 0 || N <= 0) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad shape");
   if (experts > kMaxExperts) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: experts must be <= %d", kMaxExperts);
@@ -294,6 +319,7 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
     return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: N must be a multiple of 64 for [K,N] weights, got %d", N);
   if (activation < MOE_ACT_NONE || activation > MOE_ACT_SWIGLU) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad activation");
   if (w_layout != MOE_W_KN && w_layout != MOE_W_NK) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad weight layout");
+  if (dtype != MOE_F16 && dtype != MOE_BF16) return fail(MOE_ERR_ARG, "moe_grouped_gemm: dtype must be fp16 or bf16");
   if (rows == 0) return MOE_OK;
   if (!a || !w || !c || !offsets) return fail(MOE_ERR_ARG, "moe_grouped_gemm: null pointer");
   if (!workspace || workspace_bytes < (size_t)kStatusBytes) return fail(MOE_ERR_WORKSPACE, "moe_grouped_gemm: workspace missing");
@@ -311,7 +337,9 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   p.w_kn = w_layout == MOE_W_KN;
   p.act = activation;
   p.row_scale = row_scale;
-  p.c = static_cast<__half*>(c);
+  p.c = static_cast<uint16_t*>(c);
+  p.bias = static_cast<const uint16_t*>(bias);
+  p.bf16 = dtype == MOE_BF16;
   p.status = static_cast<int32_t*>(workspace);
 
   CUtensorMap tmap_a, tmap_w;

@@ -39,6 +39,7 @@ struct RouterParams {
   int tokens, d, experts, top_k;
   int skew_experts;
   float skew_bias;
+  int bf16;  // 0: fp16 tokens / weights / logits, 1: bf16
   int epad;  // experts rounded up to the UMMA N granule (16); padded logit columns are never selected
   int kblocks, splitk, stages, tmem_cols, num_tiles;
   int32_t* idx;
@@ -64,16 +65,24 @@ constexpr int kIssuers = 6;  // lane 0 of each warp drives bulk copies in the fu
 // A logit that has been rounded to fp16 and its column pack into one 32-bit key whose unsigned
 // order is "larger value first, then lower column": high half = the fp16 bits mapped to an
 // order-preserving unsigned code (-0 folded onto +0), low half = 0xFFFF - column.
-__device__ __forceinline__ uint32_t make_key(__half h, int col) {
-  uint32_t hb = __half_as_ushort(h);
+__device__ __forceinline__ uint32_t make_key(uint32_t hb, int col) {
   if (hb == 0x8000u) hb = 0u;
   const uint32_t code = (hb & 0x8000u) ? (~hb & 0xFFFFu) : (hb | 0x8000u);
   return (code << 16) | (0xFFFFu - (uint32_t)col);
 }
-__device__ __forceinline__ float key_value(uint32_t key) {
+// Rounding to the 16-bit logit type and back (fp16 or bf16: both are sign-magnitude with the exponent
+// on top, so the same order-preserving code works for either).
+__device__ __forceinline__ uint32_t round16(float v, bool bf16) {
+  return bf16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v)) : (uint32_t)__half_as_ushort(__float2half_rn(v));
+}
+__device__ __forceinline__ float widen16(uint32_t bits, bool bf16) {
+  return bf16 ? __bfloat162float(__ushort_as_bfloat16((unsigned short)bits))
+              : __half2float(__ushort_as_half((unsigned short)bits));
+}
+__device__ __forceinline__ float key_value(uint32_t key, bool bf16) {
   const uint32_t code = key >> 16;
   const uint32_t hb = (code & 0x8000u) ? (code & 0x7FFFu) : (~code & 0xFFFFu);
-  return __half2float(__ushort_as_half((unsigned short)hb));
+  return widen16(hb, bf16);
 }
 __device__ __forceinline__ int key_column(uint32_t key) { return (int)(0xFFFFu - (key & 0xFFFFu)); }
 
@@ -95,7 +104,7 @@ __device__ __forceinline__ void key_insert(uint32_t (&keys)[KMAX], uint32_t c) {
 template <int KMAX, int S, bool WRITE_LOGITS>
 __device__ __forceinline__ void scan_columns(const float* __restrict__ prow, int E, int n_valid, int EP, int wq,
                                              int skew_experts, float skew_bias, float* __restrict__ logits_row,
-                                             uint32_t (&keys)[KMAX]) {
+                                             bool bf16, uint32_t (&keys)[KMAX]) {
 #pragma unroll
   for (int j = 0; j < KMAX; ++j) keys[j] = 0u;
   const int cols = E / 4;
@@ -110,11 +119,11 @@ __device__ __forceinline__ void scan_columns(const float* __restrict__ prow, int
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int c = c0 + u;
-      const __half h0 = __float2half_rn(acc[u]);
-      const __half h1 = __float2half_rn(__half2float(h0) + skew_bias);
-      const __half h = c < skew_experts ? h1 : h0;
+      const uint32_t h0 = round16(acc[u], bf16);
+      const uint32_t h1 = round16(widen16(h0, bf16) + skew_bias, bf16);
+      const uint32_t h = c < skew_experts ? h1 : h0;
       if (WRITE_LOGITS) {
-        if (logits_row != nullptr && c < n_valid) logits_row[c] = __half2float(h);
+        if (logits_row != nullptr && c < n_valid) logits_row[c] = widen16(h, bf16);
       }
       const uint32_t key = make_key(h, c);
       key_insert<KMAX>(keys, c < n_valid ? key : 0u);
@@ -159,13 +168,13 @@ __device__ __forceinline__ void select_phase(const RouterParams& p, const float*
     const float* prow = s_partial + (size_t)((s * S) * 32 + lane) * EP;
     uint32_t keys[KMAX];
     if (MOE_LOGITS_OUT != nullptr) {  // verification path: also writes the logits
-      if (S == 4) scan_columns<KMAX, 4, true>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, keys);
-      else if (S == 2) scan_columns<KMAX, 2, true>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, keys);
-      else scan_columns<KMAX, 1, true>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, keys);
+      if (S == 4) scan_columns<KMAX, 4, true>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, p.bf16 != 0, keys);
+      else if (S == 2) scan_columns<KMAX, 2, true>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, p.bf16 != 0, keys);
+      else scan_columns<KMAX, 1, true>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, p.bf16 != 0, keys);
     } else {
-      if (S == 4) scan_columns<KMAX, 4, false>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, keys);
-      else if (S == 2) scan_columns<KMAX, 2, false>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, keys);
-      else scan_columns<KMAX, 1, false>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, keys);
+      if (S == 4) scan_columns<KMAX, 4, false>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, p.bf16 != 0, keys);
+      else if (S == 2) scan_columns<KMAX, 2, false>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, p.bf16 != 0, keys);
+      else scan_columns<KMAX, 1, false>(prow, E, EL, EP, wq, p.skew_experts, p.skew_bias, lo, p.bf16 != 0, keys);
     }
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) s_cand[((s * 4 + wq) * KMAX + j) * 32 + lane] = keys[j];
@@ -185,10 +194,10 @@ __device__ __forceinline__ void select_phase(const RouterParams& p, const float*
       for (int j = 0; j < KMAX; ++j) key_insert<KMAX>(keys, s_cand[((s * 4 + w4) * KMAX + j) * 32 + lane]);
     float e[KMAX];
     float sum = 0.f;
-    const float v0 = key_value(keys[0]);
+    const float v0 = key_value(keys[0], p.bf16 != 0);
 #pragma unroll
     for (int j = 0; j < KMAX; ++j)
-      if (j < p.top_k) { e[j] = expf(key_value(keys[j]) - v0); sum += e[j]; }
+      if (j < p.top_k) { e[j] = expf(key_value(keys[j], p.bf16 != 0) - v0); sum += e[j]; }
     const float inv = 1.f / fmaxf(sum, 1e-9f);
 #pragma unroll
     for (int j = 0; j < KMAX; ++j)
@@ -311,7 +320,7 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(kBlockM, E, 0, 0, 0);
+      const uint32_t idesc = make_idesc_f16(kBlockM, E, p.bf16, 0, 0);
       for (int i = 0; i < nkb; ++i) {
         const int s = i % p.stages;
         const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
@@ -457,7 +466,7 @@ bool fused_enabled() {
 // 4-way K split and every cluster of the grid resident at once, otherwise the plain kernel runs
 // and the caller launches the scatter.
 int launch_router(const void* x, const void* w, int tokens, int d, int experts, int top_k, int skew_experts,
-                  float skew_bias, int32_t* idx, float* gates, float* logits_out, const Workspace& ws,
+                  float skew_bias, int dtype, int32_t* idx, float* gates, float* logits_out, const Workspace& ws,
                   cudaStream_t stream, const FusedPack* fp = nullptr, bool* did_fuse = nullptr) {
   if (did_fuse) *did_fuse = false;
   CUtensorMap tmap_x, tmap_w;
@@ -469,6 +478,7 @@ int launch_router(const void* x, const void* w, int tokens, int d, int experts, 
 
   RouterParams p;
   p.tokens = tokens; p.d = d; p.experts = experts; p.top_k = top_k; p.epad = epad;
+  p.bf16 = dtype == MOE_BF16;
   p.skew_experts = skew_experts < 0 ? 0 : (skew_experts > experts ? experts : skew_experts);
   p.skew_bias = skew_bias;
   if (skew_bias == 0.0f) p.skew_experts = 0;
@@ -558,8 +568,10 @@ int launch_router(const void* x, const void* w, int tokens, int d, int experts, 
 }
 
 int check_router_args(const char* who, const void* x, const void* w, int tokens, int d, int experts, int top_k,
-                      const void* idx, const void* gates, const void* workspace, size_t workspace_bytes) {
+                      int dtype, const void* idx, const void* gates, const void* workspace,
+                      size_t workspace_bytes) {
   if (tokens < 0 || d <= 0 || experts <= 0) return fail(MOE_ERR_ARG, "%s: bad shape", who);
+  if (dtype != MOE_F16 && dtype != MOE_BF16) return fail(MOE_ERR_ARG, "%s: x must be fp16 or bf16", who);
   if (top_k < 1 || top_k > 8) return fail(MOE_ERR_UNSUPPORTED, "%s: top_k must be in [1,8], got %d", who, top_k);
   if (top_k > experts) return fail(MOE_ERR_ARG, "%s: top_k must be <= n_experts", who);
   if (experts > 256) return fail(MOE_ERR_UNSUPPORTED, "%s: experts must be <= 256, got %d", who, experts);
@@ -579,24 +591,24 @@ int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int t
 
 }  // namespace moe
 
-extern "C" int moe_router_gemm_select(const void* x, const void* w_router, int tokens, int d, int experts,
+extern "C" int moe_router_gemm_select(const void* x, const void* w_router, int dtype, int tokens, int d, int experts,
                                       int top_k, int skew_experts, float skew_bias, int32_t* idx, float* gates,
                                       float* logits_out, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace moe;
-  int rc = check_router_args("moe_router_gemm_select", x, w_router, tokens, d, experts, top_k, idx, gates,
+  int rc = check_router_args("moe_router_gemm_select", x, w_router, tokens, d, experts, top_k, dtype, idx, gates,
                              workspace, workspace_bytes);
   if (rc != MOE_OK || tokens == 0) return rc;
   Workspace ws = carve(workspace, tokens, experts);
-  return launch_router(x, w_router, tokens, d, experts, top_k, skew_experts, skew_bias, idx, gates, logits_out, ws,
-                       static_cast<cudaStream_t>(stream));
+  return launch_router(x, w_router, tokens, d, experts, top_k, skew_experts, skew_bias, dtype, idx, gates, logits_out,
+                       ws, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int moe_route_fused(const void* x, const void* w_router, int tokens, int d, int experts, int top_k,
+extern "C" int moe_route_fused(const void* x, const void* w_router, int dtype, int tokens, int d, int experts, int top_k,
                                int skew_experts, float skew_bias, int32_t* idx, float* gates, int32_t* counts,
                                int32_t* offsets, void* packed, int32_t* row_route, int32_t* route_row,
                                float* logits_out, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace moe;
-  int rc = check_router_args("moe_route_fused", x, w_router, tokens, d, experts, top_k, idx, gates, workspace,
+  int rc = check_router_args("moe_route_fused", x, w_router, tokens, d, experts, top_k, dtype, idx, gates, workspace,
                              workspace_bytes);
   if (rc != MOE_OK) return rc;
   if (!counts || !offsets || (tokens > 0 && !row_route)) return fail(MOE_ERR_ARG, "moe_route_fused: null pointer");
@@ -605,8 +617,8 @@ extern "C" int moe_route_fused(const void* x, const void* w_router, int tokens, 
   if (tokens > 0) {
     FusedPack fp{packed, counts, offsets, row_route, route_row};
     bool fused = false;
-    rc = launch_router(x, w_router, tokens, d, experts, top_k, skew_experts, skew_bias, idx, gates, logits_out, ws, s,
-                       &fp, &fused);
+    rc = launch_router(x, w_router, tokens, d, experts, top_k, skew_experts, skew_bias, dtype, idx, gates, logits_out,
+                       ws, s, &fp, &fused);
     if (rc != MOE_OK || fused) return rc;
   }
   return launch_scan_scatter(x, 2, idx, tokens, d, experts, top_k, counts, offsets, packed, row_route, route_row,

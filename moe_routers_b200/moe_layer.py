@@ -8,7 +8,7 @@ forward body is the fused B200 path:
     ->  gate-weighted combine
 
 instead of `index_select` / `argsort` / a Python loop with one `.item()` sync per
-expert / `index_add_`.  It runs in fp16 on CUDA only.
+expert / `index_add_`.  It runs in fp16 or bf16 on CUDA only.
 """
 from __future__ import annotations
 
@@ -81,8 +81,8 @@ class MoELayer(torch.nn.Module):
         bsz, seq_len, d_model = x.shape
         if not x.is_cuda:
             raise RuntimeError("inputs must be CUDA")
-        if x.dtype != torch.float16 or self.router.weight.dtype != torch.float16:
-            raise RuntimeError("x must be fp16 (Half)")
+        if x.dtype not in (torch.float16, torch.bfloat16) or self.router.weight.dtype != x.dtype:
+            raise RuntimeError("x and the layer's weights must both be fp16 (Half) or both bf16")
         flat = x.reshape(-1, d_model)
         e, k = self.n_experts, self.top_k
         fused = type(self.router_impl) is CUDATopKRouter and e <= 256 and k <= 8 and d_model % 8 == 0

@@ -119,8 +119,8 @@ def router_gemm_select(x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, s
                        skew_bias: float = 0.0, return_logits: bool = False):
     """Fused logit GEMM + skew + top-k + gates.  Returns (idx, gates[, logits fp32])."""
     _require_cuda(x, w_router)
-    if x.dtype != torch.float16 or w_router.dtype != torch.float16:
-        raise RuntimeError("x must be fp16 (Half)")
+    if x.dtype not in (torch.float16, torch.bfloat16) or w_router.dtype != x.dtype:
+        raise RuntimeError("x and the router weight must both be fp16 (Half) or both bf16")
     x = x.contiguous()
     w_router = w_router.contiguous()
     t, d = x.shape
@@ -131,7 +131,7 @@ def router_gemm_select(x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, s
         gates = torch.empty((t, top_k), dtype=torch.float32, device=dev)
         logits = torch.empty((t, e), dtype=torch.float32, device=dev) if return_logits else None
         ws = workspace(dev, t, e, top_k)
-        check(lib.moe_router_gemm_select(x.data_ptr(), w_router.data_ptr(), t, d, e, int(top_k),
+        check(lib.moe_router_gemm_select(x.data_ptr(), w_router.data_ptr(), _DTYPE_CODE[x.dtype], t, d, e, int(top_k),
                                          int(skew_experts), float(skew_bias), idx.data_ptr(),
                                          gates.data_ptr(), logits.data_ptr() if return_logits else None,
                                          ws.data_ptr(), ws.numel(), _stream()))
@@ -147,8 +147,8 @@ def route_fused(x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, skew_exp
     from a previous call to avoid re-allocation.
     """
     _require_cuda(x, w_router)
-    if x.dtype != torch.float16 or w_router.dtype != torch.float16:
-        raise RuntimeError("x must be fp16 (Half)")
+    if x.dtype not in (torch.float16, torch.bfloat16) or w_router.dtype != x.dtype:
+        raise RuntimeError("x and the router weight must both be fp16 (Half) or both bf16")
     x = x.contiguous()
     w_router = w_router.contiguous()
     t, d = x.shape
@@ -167,7 +167,7 @@ def route_fused(x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, skew_exp
         if return_logits and "logits" not in o:
             o["logits"] = torch.empty((t, e), dtype=torch.float32, device=dev)
         ws = workspace(dev, t, e, top_k)
-        check(lib.moe_route_fused(x.data_ptr(), w_router.data_ptr(), t, d, e, int(top_k),
+        check(lib.moe_route_fused(x.data_ptr(), w_router.data_ptr(), _DTYPE_CODE[x.dtype], t, d, e, int(top_k),
                                   int(skew_experts), float(skew_bias), o["idx"].data_ptr(),
                                   o["gates"].data_ptr(), o["counts"].data_ptr(), o["offsets"].data_ptr(),
                                   o["packed"].data_ptr(), o["row_route"].data_ptr(),
@@ -204,16 +204,20 @@ _ACT = {None: _lib.MOE_ACT_NONE, "none": _lib.MOE_ACT_NONE, "gelu": _lib.MOE_ACT
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, layout: str = "nk",
                  activation: Optional[str] = None, row_scale: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None, sm_margin: int = 0) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, sm_margin: int = 0,
+                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """c[offsets[e]:offsets[e+1]] = act(a[offsets[e]:offsets[e+1]] @ W[e]) for every expert.
 
-    a [rows, K] fp16; w [E, N, K] (layout "nk") or [E, K, N] (layout "kn"), fp16;
-    offsets int32 [E+1] on the device.  With activation "swiglu" the weight has
+    a [rows, K]; w [E, N, K] (layout "nk") or [E, K, N] (layout "kn"); both fp16 or both bf16;
+    offsets int32 [E+1] on the device; bias [E, output features] (same dtype) is added before the
+    activation.  With activation "swiglu" the weight has
     2N output features (gate rows first, then up) and the result has N columns.
     """
     _require_cuda(a, w, offsets)
-    if a.dtype != torch.float16 or w.dtype != torch.float16:
-        raise RuntimeError("grouped_gemm: a and w must be fp16")
+    if a.dtype not in (torch.float16, torch.bfloat16) or w.dtype != a.dtype:
+        raise RuntimeError("grouped_gemm: a and w must both be fp16 or both bf16")
+    if bias is not None and (bias.dtype != a.dtype or not bias.is_cuda):
+        raise RuntimeError("grouped_gemm: bias must be a CUDA tensor of the same dtype")
     if w.dim() != 3:
         raise RuntimeError("grouped_gemm: w must be [E, N, K] or [E, K, N]")
     a = a.contiguous()
@@ -233,6 +237,8 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, lay
         rs = row_scale.to(torch.float32).contiguous() if row_scale is not None else None
         check(lib.moe_grouped_gemm(a.data_ptr(), w.data_ptr(), c.data_ptr(), offsets.data_ptr(), e, rows,
                                    k_dim, n_out, _lib.MOE_W_NK if layout == "nk" else _lib.MOE_W_KN,
-                                   w.stride(0), act, rs.data_ptr() if rs is not None else None, int(sm_margin),
+                                   w.stride(0), act, rs.data_ptr() if rs is not None else None,
+                                   bias.contiguous().data_ptr() if bias is not None else None,
+                                   _DTYPE_CODE[a.dtype], int(sm_margin),
                                    ws.data_ptr(), ws.numel(), _stream()))
     return c

@@ -114,3 +114,64 @@ def test_grouped_gemm_row_scale_and_benchmark_shape(ops):
             ref[lo:hi] = oracle.gelu_ffn(x[lo:hi].numpy(), w1[e].numpy(), w2[e].numpy(), layout="nk").astype(np.float32)
     ref *= scale.numpy()[:, None]
     np.testing.assert_allclose(y.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype,layout,act", [(torch.bfloat16, "nk", "gelu"), (torch.bfloat16, "kn", None),
+                                              (torch.float16, "nk", "silu"), (torch.float16, "kn", "swiglu"),
+                                              (torch.bfloat16, "nk", "swiglu")])
+def test_grouped_gemm_bias_and_bf16(ops, dtype, layout, act):
+    counts = [70, 0, 129, 5]
+    e, K, N = len(counts), 256, 128
+    off = _segments(counts)
+    rows = int(off[-1])
+    g = torch.Generator().manual_seed(7)
+    a = torch.randn(rows, K, generator=g).to(dtype)
+    n_w = 2 * N if act == "swiglu" else N
+    shape = (e, n_w, K) if layout == "nk" else (e, K, n_w)
+    w = (torch.randn(*shape, generator=g) / K ** 0.5).to(dtype)
+    bias = (torch.randn(e, n_w, generator=g) * 0.5).to(dtype)
+    out = ops.grouped_gemm(a.cuda(), w.cuda(), torch.from_numpy(off).cuda(), layout=layout, activation=act,
+                           bias=bias.cuda())
+    assert out.dtype == dtype and ops.read_status() == 0
+    ref = torch.zeros(rows, N)
+    for ex in range(e):
+        lo, hi = off[ex], off[ex + 1]
+        we = w[ex].float().t() if layout == "nk" else w[ex].float()
+        y = a[lo:hi].float() @ we + bias[ex].float()
+        if act == "gelu":
+            y = torch.nn.functional.gelu(y)
+        elif act == "silu":
+            y = torch.nn.functional.silu(y)
+        elif act == "swiglu":
+            y = torch.nn.functional.silu(y[:, :N]) * y[:, N:]
+        ref[lo:hi] = y
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3  # one rounding to the storage type
+    scale = float(ref.abs().max())
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=tol * scale)
+
+
+def test_demo_pipeline_on_device(ops):
+    """The reference's demo (fused_select.py:43-99: route, split by counts on the host, GEMM + bias + SiLU,
+    GEMM + bias, concatenate) as three device-side calls without any host read of the counts."""
+    t, d, h, e = 600, 256, 384, 64
+    g = torch.Generator().manual_seed(42)
+    logits = torch.randn(t, e, generator=g).half()
+    x = torch.randn(t, d, generator=g).half()
+    w1 = (torch.randn(e, d, h, generator=g) * 0.02).half()
+    b1 = (torch.randn(e, h, generator=g) * 0.01).half()
+    w2 = (torch.randn(e, h, d, generator=g) * 0.02).half()
+    b2 = (torch.randn(e, d, generator=g) * 0.01).half()
+    idx, gates = ops.topk_select(logits.cuda(), 2)
+    counts, offsets, packed, row_route, route_row = ops.pack(x.cuda(), idx, e)
+    hid = ops.grouped_gemm(packed, w1.cuda(), offsets, layout="kn", activation="silu", bias=b1.cuda())
+    out = ops.grouped_gemm(hid, w2.cuda(), offsets, layout="kn", bias=b2.cuda())
+    assert tuple(out.shape) == (2 * t, d)
+    off = offsets.cpu().numpy()
+    pk = packed.float().cpu()
+    ref = torch.zeros(2 * t, d)
+    for ex in range(e):
+        lo, hi = off[ex], off[ex + 1]
+        if hi > lo:
+            hh = torch.nn.functional.silu(pk[lo:hi] @ w1[ex].float() + b1[ex].float()).half().float()
+            ref[lo:hi] = hh @ w2[ex].float() + b2[ex].float()
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=2e-3)

@@ -90,3 +90,26 @@ def test_route_fused_matches_two_step_path(ops):
     torch.testing.assert_close(g2, o["gates"], rtol=1e-6, atol=1e-7)
     c, off, packed, rr, inv = ops.pack(xc, idx2, 64)
     assert torch.equal(packed, o["packed"]) and torch.equal(off, o["offsets"]) and torch.equal(rr, o["row_route"])
+
+
+@pytest.mark.parametrize("t,d,e,k,skew_n,skew_b", [(1000, 1024, 64, 2, 8, 2.0), (300, 512, 48, 4, 0, 0.0)])
+def test_route_fused_bf16(ops, t, d, e, k, skew_n, skew_b):
+    """bf16 tokens and router weight: logits are rounded to bf16 (the dtype the reference's
+    `x @ w.t()` yields for bf16 inputs); the selection is bit-exact given those logits."""
+    g = torch.Generator().manual_seed(t + e)
+    x = torch.randn(t, d, generator=g).bfloat16()
+    w = (torch.randn(e, d, generator=g) / d ** 0.5).bfloat16()
+    o = ops.route_fused(x.cuda(), w.cuda(), k, skew_experts=skew_n, skew_bias=skew_b, return_logits=True)
+    assert ops.read_status() == 0
+    ref = (x.float() @ w.float().t()).bfloat16()
+    if skew_n:
+        ref[:, :skew_n] += skew_b
+    logits = o["logits"].cpu()
+    # one bf16 ulp (2^-8 relative), twice when the skew add rounds again
+    torch.testing.assert_close(logits, ref.float(), rtol=2 ** -7, atol=2 ** -7)
+    ref_idx, ref_g, _ = oracle.topk_select(logits.numpy(), k)
+    np.testing.assert_array_equal(o["idx"].cpu().numpy(), ref_idx.astype(np.int32))
+    np.testing.assert_allclose(o["gates"].cpu().numpy(), ref_g, rtol=1e-5, atol=1e-7)
+    packed, counts, offsets, row_route, _ = oracle.pack_canonical(x.view(torch.int16).numpy(), ref_idx, e)
+    np.testing.assert_array_equal(o["packed"].view(torch.int16).cpu().numpy(), packed)
+    np.testing.assert_array_equal(o["offsets"].cpu().numpy(), offsets)
