@@ -13,6 +13,7 @@ Prints ONE JSON line (rank 0).  Keys beyond the common contract:
   roofline      dominant kernel (the pack scatter), algorithmic bytes per launch / its average
                 duration from CUDA events, against the measured HBM copy peak
   route_roofline the same fraction for the whole step (101,253,636 algorithmic bytes)
+  select_pack_roofline the reference's own operator (logits given): select + count + scan + pack
   cpu_baseline  the reference's CPU routing path (torch port in oracle/cpu_route.py) on the
                 host cores, a bounded sample of the same workload
   e2e           the same metric through the public API with HOST buffers (pinned), host<->device
@@ -200,6 +201,21 @@ def main_ours(args):
     def step(i):
         ops.route_fused(xs[i % n_sets], w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B, out=outs[i % n_sets])
 
+    # the reference's own operator: logits given (fp16), select + count + scan + pack
+    lgs = [(xs[i] @ w.t()) for i in range(n_sets)]
+    for lg in lgs:
+        lg[:, :SKEW_N] += SKEW_B
+    sp_outs = [ops.fused_select(lgs[i], xs[i], E, K_TOP) for i in range(n_sets)]
+
+    def select_pack(i):
+        ops.fused_select(lgs[i % n_sets], xs[i % n_sets], E, K_TOP, out=sp_outs[i % n_sets])
+
+    def scatter_only(i):
+        # the scatter kernel alone: tokens, indices and tile histograms of set 0 (the tokens are then
+        # L2-resident, as they are right after the router kernel in the fused step), output rows into
+        # rotating buffers so that every launch writes cold memory
+        ops.pack_scatter(xs[0], E, dict(outs[0], packed=outs[i % n_sets]["packed"]))
+
     def select_only(i):
         ops.router_gemm_select(xs[i % n_sets], w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B)
 
@@ -238,6 +254,9 @@ def main_ours(args):
     torch.cuda.synchronize()
     g_route = capture(step, steps)
     g_select = capture(select_only, steps)
+    g_selpack = capture(select_pack, steps)
+    ops.route_fused(xs[0], w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B, out=outs[0])  # histograms of set 0
+    g_scatter = capture(scatter_only, steps)
     g_route.replay()  # one untimed replay: graph upload
     torch.cuda.synchronize()
 
@@ -251,9 +270,16 @@ def main_ours(args):
     torch.cuda.synchronize()
     sampler.stop()
     select_ms = timed(g_select)
+    selpack_us = timed(g_selpack) / steps * 1e3
+    ops.route_fused(xs[0], w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B, out=outs[0])
+    scatter_direct_us = timed(g_scatter) / steps * 1e3
 
     ms_per_step = total_ms / steps
     select_us = select_ms / steps * 1e3
+    # Duration of the scatter kernel inside the timed region: fused step minus the router kernel.
+    # (Launched alone back to back it is slower, see `alone_back_to_back_us`: its 67 MB of stores are
+    # absorbed by the L2 and written back to DRAM under the NEXT kernel; with nothing but scatters in
+    # the queue the write-back has no read phase to hide under and write-only HBM bandwidth governs.)
     scatter_us = max(ms_per_step * 1e3 - select_us, 1e-3)
     value = world * T / (ms_per_step * 1e-3)
     peak, peak_kind = measured_peak_gbs()
@@ -298,7 +324,7 @@ def main_ours(args):
 
         from moe_routers_b200 import bench_ep
 
-        del xs, sel_outs
+        del xs, sel_outs, lgs, sp_outs
         torch.cuda.empty_cache()
         for tag, (sn, sb) in {"skew": (SKEW_N, SKEW_B), "plain": (0, 0.0)}.items():
             ns = _ap.Namespace(experts=E, top_k=K_TOP, d_model=D, hidden=8192, tokens=T, all_strategies=False,
@@ -325,13 +351,21 @@ def main_ours(args):
             "config": {"workload": WORKLOAD, "tokens_per_gpu": T, "d_model": D, "experts": E, "top_k": K_TOP,
                        "l2": f"{n_sets} rotating input/output sets, {n_sets * (T * D * 2 * 3) >> 20} MiB > 126 MB L2",
                        "launch": "K steps captured in one CUDA graph"},
-            "breakdown_us": {"t_logit_select": select_us, "t_pack": scatter_us, "t_route": ms_per_step * 1e3},
+            "breakdown_us": {"t_logit_select": select_us, "t_pack": ms_per_step * 1e3 - select_us,
+                             "t_route": ms_per_step * 1e3},
             "roofline": {"kernel": "pack_scatter_bulk_kernel", "bound": "hbm", "achieved": pack_gbs, "peak": peak,
                          "unit": "GB/s", "frac": pack_gbs / peak, "traffic": SCATTER_DRAM_TRAFFIC, "peak_kind": peak_kind,
                          "algorithmic_bytes": PACK_BYTES,
-                         "duration_us": scatter_us, "how": "events: K fused steps minus K router-kernel-only steps"},
+                         "duration_us": scatter_us,
+                         "how": "CUDA events, same run: K fused steps minus K router-kernel-only steps (both one graph)",
+                         "alone_back_to_back_us": scatter_direct_us},
             "route_roofline": {"bound": "hbm", "achieved": route_gbs, "peak": peak, "unit": "GB/s",
                                "frac": route_gbs / peak, "algorithmic_bytes": ROUTE_BYTES},
+            "select_pack_roofline": {
+                "what": "fused_select_forward(logits, x): select + count + scan + pack from given fp16 logits, 2 launches",
+                "bound": "hbm", "duration_us": selpack_us, "algorithmic_bytes": PACK_BYTES + T * E * 2 + T * K_TOP * 4,
+                "achieved": (PACK_BYTES + T * E * 2 + T * K_TOP * 4) / (selpack_us * 1e-6) / 1e9, "peak": peak,
+                "unit": "GB/s", "frac": (PACK_BYTES + T * E * 2 + T * K_TOP * 4) / (selpack_us * 1e-6) / 1e9 / peak},
             "e2e": {"value": world * T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
             "gpu_launches": 2 * steps,

@@ -98,6 +98,29 @@ int moe_pack(const void* x, int elem_bytes, const int32_t* idx, int tokens, int 
              int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Select + count + scan + pack from given logits: the reference's whole operator
+ * fused_select_forward(logits, x) (kernels/fused_select.cu:203-311: five kernels, two memsets,
+ * six allocations and one host round trip) as two launches: the select kernel also writes the
+ * per-tile expert histograms, the scatter derives offsets from them.  Arguments as in
+ * moe_topk_select and moe_pack; any experts <= 1024 and top_k <= 8.
+ */
+int moe_fused_select(const void* logits, int logits_dtype, const void* x, int elem_bytes, int tokens, int d,
+                     int experts, int top_k, int32_t* idx, float* gates, int32_t* counts, int32_t* offsets,
+                     void* packed, int32_t* row_route, int32_t* route_row, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/*
+ * The scatter half of the pack on its own (offsets, ranks and row copies), reading the per-tile
+ * histograms that a preceding moe_router_gemm_select / moe_route_fused / moe_fused_select call with
+ * the same workspace, token count and expert count left in the workspace.  It is what
+ * moe_route_fused launches second; exposed so that the stage can be driven and timed by itself
+ * (T_pack of bench_router.py:547-552).  Arguments as in moe_pack.
+ */
+int moe_pack_scatter(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+                     int top_k, int32_t* counts, int32_t* offsets, void* packed, int32_t* row_route,
+                     int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * moe_pack for callers that cannot allocate.  (No counterpart in the reference.)
  * Same inputs, outputs and ordering as moe_pack, but the scratch that moe_pack takes from a
  * caller-owned workspace comes from a 256 KiB array built into the library image, so the call

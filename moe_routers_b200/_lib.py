@@ -29,6 +29,8 @@ SIGNATURES = {
     "moe_read_status": (_i, [_p, _p, C.POINTER(C.c_int)]),
     "moe_topk_select": (_i, [_p, _i, _i, _i, _i, _p, _p, _p]),
     "moe_pack": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "moe_fused_select": (_i, [_p, _i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "moe_pack_scatter": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "moe_pack_static": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p]),
     "moe_combine": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _p]),
     "moe_route_fused": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),

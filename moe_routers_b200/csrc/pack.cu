@@ -455,3 +455,56 @@ extern "C" int moe_pack_static(const void* x, int elem_bytes, const int32_t* idx
   return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, packed, row_route,
                              route_row, ws, s);
 }
+
+namespace moe {
+int launch_select_any(const void* logits, int logits_dtype, int tokens, int experts, int top_k, int32_t* idx,
+                      float* gates, int32_t* tile_hist, cudaStream_t s);
+}
+
+// The reference's whole operator in two launches: select (+ tile histograms), then scatter.
+extern "C" int moe_fused_select(const void* logits, int logits_dtype, const void* x, int elem_bytes, int tokens,
+                                int d, int experts, int top_k, int32_t* idx, float* gates, int32_t* counts,
+                                int32_t* offsets, void* packed, int32_t* row_route, int32_t* route_row,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace moe;
+  if (tokens < 0 || d <= 0 || experts <= 0) return fail(MOE_ERR_ARG, "moe_fused_select: bad shape");
+  if (top_k < 1 || top_k > 8) return fail(MOE_ERR_UNSUPPORTED, "moe_fused_select: top_k must be in [1,8], got %d", top_k);
+  if (top_k > experts) return fail(MOE_ERR_ARG, "moe_fused_select: top_k must be <= n_experts");
+  if (experts > 1024) return fail(MOE_ERR_UNSUPPORTED, "moe_fused_select: experts must be <= 1024");
+  if (elem_bytes != 2 && elem_bytes != 4) return fail(MOE_ERR_ARG, "moe_fused_select: elem_bytes must be 2 or 4");
+  if (!counts || !offsets) return fail(MOE_ERR_ARG, "moe_fused_select: null counts/offsets");
+  if (tokens > 0 && (!logits || !idx || !gates || !row_route || (packed && !x)))
+    return fail(MOE_ERR_ARG, "moe_fused_select: null pointer");
+  if (!workspace || workspace_bytes < workspace_bytes_for(tokens, experts, top_k))
+    return fail(MOE_ERR_WORKSPACE, "moe_fused_select: workspace too small (need %zu bytes)",
+                workspace_bytes_for(tokens, experts, top_k));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Workspace ws = carve(workspace, tokens, experts);
+  if (tokens > 0) {
+    const int rc = launch_select_any(logits, logits_dtype, tokens, experts, top_k, idx, gates, ws.tile_hist, s);
+    if (rc != MOE_OK) return rc;
+  }
+  return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, packed, row_route,
+                             route_row, ws, s);
+}
+
+// The scatter half on its own: offsets + ranks + row copies from tile histograms that a preceding
+// call (moe_router_gemm_select, moe_route_fused or moe_fused_select with the same workspace, token
+// count and expert count) left in the workspace.
+extern "C" int moe_pack_scatter(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+                                int top_k, int32_t* counts, int32_t* offsets, void* packed, int32_t* row_route,
+                                int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace moe;
+  if (tokens < 0 || d <= 0 || experts <= 0) return fail(MOE_ERR_ARG, "moe_pack_scatter: bad shape");
+  if (top_k < 1 || top_k > 8) return fail(MOE_ERR_UNSUPPORTED, "moe_pack_scatter: top_k must be in [1,8], got %d", top_k);
+  if (experts > 1024) return fail(MOE_ERR_UNSUPPORTED, "moe_pack_scatter: experts must be <= 1024");
+  if (elem_bytes != 2 && elem_bytes != 4) return fail(MOE_ERR_ARG, "moe_pack_scatter: elem_bytes must be 2 or 4");
+  if (!counts || !offsets) return fail(MOE_ERR_ARG, "moe_pack_scatter: null counts/offsets");
+  if (tokens > 0 && (!idx || !row_route || (packed && !x))) return fail(MOE_ERR_ARG, "moe_pack_scatter: null pointer");
+  if (!workspace || workspace_bytes < workspace_bytes_for(tokens, experts, top_k))
+    return fail(MOE_ERR_WORKSPACE, "moe_pack_scatter: workspace too small (need %zu bytes)",
+                workspace_bytes_for(tokens, experts, top_k));
+  Workspace ws = carve(workspace, tokens, experts);
+  return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, packed, row_route,
+                             route_row, ws, static_cast<cudaStream_t>(stream));
+}

@@ -16,13 +16,21 @@ namespace {
 
 constexpr int kWarpsPerCta = 8;
 
-template <typename T, int NPL>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+// WARPS rows per CTA.  With HIST the CTA covers exactly one 32-token tile (WARPS == kTileTokens) and
+// also writes that tile's per-expert histogram, which the pack consumes: select + count in one launch.
+template <typename T, int NPL, int WARPS, bool HIST>
+__global__ void __launch_bounds__(WARPS * 32)
 topk_select_kernel(const T* __restrict__ logits, int32_t* __restrict__ out_idx,
-                   float* __restrict__ out_w, int tokens, int experts, int top_k) {
+                   float* __restrict__ out_w, int tokens, int experts, int top_k,
+                   int32_t* __restrict__ tile_hist) {
+  extern __shared__ int32_t s_hist[];  // [experts], HIST only
   const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  if (row >= tokens) return;  // whole warp leaves together
+  const int row = blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (HIST) {
+    for (int e = threadIdx.x; e < experts; e += WARPS * 32) s_hist[e] = 0;
+    __syncthreads();
+  }
+  if (row < tokens) {
   const T* src = logits + (size_t)row * experts;
 
   float v[NPL];
@@ -74,29 +82,53 @@ topk_select_kernel(const T* __restrict__ logits, int32_t* __restrict__ out_idx,
       if (j < top_k) {
         out_idx[(size_t)row * top_k + j] = pick_i[j];
         out_w[(size_t)row * top_k + j] = e[j] * inv;
+        if (HIST) atomicAdd(&s_hist[pick_i[j]], 1);
       }
+  }
+  }  // row < tokens
+  if (HIST) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += WARPS * 32) tile_hist[(size_t)blockIdx.x * experts + e] = s_hist[e];
   }
 }
 
 template <typename T>
 int launch_select(const void* logits, int tokens, int experts, int top_k, int32_t* idx, float* w,
-                  cudaStream_t s) {
-  const int grid = (tokens + kWarpsPerCta - 1) / kWarpsPerCta;
+                  int32_t* tile_hist, cudaStream_t s) {
   const T* p = static_cast<const T*>(logits);
   const int npl = (experts + 31) / 32;
-#define MOE_SEL(N)                                                                         \
-  topk_select_kernel<T, N><<<grid, kWarpsPerCta * 32, 0, s>>>(p, idx, w, tokens, experts, top_k)
-  if (npl <= 1) MOE_SEL(1);
-  else if (npl <= 2) MOE_SEL(2);
-  else if (npl <= 4) MOE_SEL(4);
-  else if (npl <= 8) MOE_SEL(8);
-  else if (npl <= 16) MOE_SEL(16);
-  else MOE_SEL(32);
+  const bool hist = tile_hist != nullptr;
+  const int grid = hist ? (tokens + kTileTokens - 1) / kTileTokens : (tokens + kWarpsPerCta - 1) / kWarpsPerCta;
+#define MOE_SEL(N)                                                                                     \
+  if (hist)                                                                                            \
+    topk_select_kernel<T, N, kTileTokens, true><<<grid, kTileTokens * 32, experts * sizeof(int32_t), s>>>( \
+        p, idx, w, tokens, experts, top_k, tile_hist);                                                 \
+  else                                                                                                 \
+    topk_select_kernel<T, N, kWarpsPerCta, false><<<grid, kWarpsPerCta * 32, 0, s>>>(p, idx, w, tokens, experts, \
+                                                                                    top_k, nullptr)
+  if (npl <= 1) { MOE_SEL(1); }
+  else if (npl <= 2) { MOE_SEL(2); }
+  else if (npl <= 4) { MOE_SEL(4); }
+  else if (npl <= 8) { MOE_SEL(8); }
+  else if (npl <= 16) { MOE_SEL(16); }
+  else { MOE_SEL(32); }
 #undef MOE_SEL
   return check_launch("topk_select_kernel");
 }
 
 }  // namespace
+
+// select (+ per-tile histogram when tile_hist is given) for any logits dtype
+int launch_select_any(const void* logits, int logits_dtype, int tokens, int experts, int top_k, int32_t* idx,
+                      float* gates, int32_t* tile_hist, cudaStream_t s) {
+  switch (logits_dtype) {
+    case MOE_F16: return launch_select<__half>(logits, tokens, experts, top_k, idx, gates, tile_hist, s);
+    case MOE_BF16: return launch_select<__nv_bfloat16>(logits, tokens, experts, top_k, idx, gates, tile_hist, s);
+    case MOE_F32: return launch_select<float>(logits, tokens, experts, top_k, idx, gates, tile_hist, s);
+    default: return fail(MOE_ERR_ARG, "logits must be fp16/bf16/fp32");
+  }
+}
+
 }  // namespace moe
 
 extern "C" int moe_topk_select(const void* logits, int logits_dtype, int tokens, int experts,
@@ -108,11 +140,6 @@ extern "C" int moe_topk_select(const void* logits, int logits_dtype, int tokens,
   if (experts > 1024) return fail(MOE_ERR_UNSUPPORTED, "moe_topk_select: experts must be <= 1024, got %d", experts);
   if (tokens == 0) return MOE_OK;
   if (!logits || !idx || !gates) return fail(MOE_ERR_ARG, "moe_topk_select: null pointer");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (logits_dtype) {
-    case MOE_F16: return launch_select<__half>(logits, tokens, experts, top_k, idx, gates, s);
-    case MOE_BF16: return launch_select<__nv_bfloat16>(logits, tokens, experts, top_k, idx, gates, s);
-    case MOE_F32: return launch_select<float>(logits, tokens, experts, top_k, idx, gates, s);
-    default: return fail(MOE_ERR_ARG, "moe_topk_select: logits must be fp16/bf16/fp32");
-  }
+  return launch_select_any(logits, logits_dtype, tokens, experts, top_k, idx, gates, nullptr,
+                           static_cast<cudaStream_t>(stream));
 }

@@ -47,8 +47,7 @@ def fused_select_forward(logits: torch.Tensor, x: torch.Tensor):
         raise RuntimeError("x must be contiguous")
     if x.size(1) <= 0:
         raise RuntimeError("d_model must be > 0")
-    idx, w = ops.topk_select(logits, K)
-    counts, offsets, packed, _row_route, _route_row = ops.pack(x, idx, E)
+    idx, w, counts, offsets, packed, _row_route, _route_row = ops.fused_select(logits, x, E, K)
     return idx, w, counts, offsets, packed
 
 

@@ -98,6 +98,50 @@ def pack(x: torch.Tensor, idx: torch.Tensor, experts: int, *, copy_rows: bool = 
     return counts, offsets, packed, row_route, route_row
 
 
+def pack_scatter(x: torch.Tensor, experts: int, out: dict) -> dict:
+    """Re-run only the scatter half of `route_fused` into the buffers of `out` (a dict returned by
+    route_fused for the same x): the tile histograms of that call must still be in the workspace."""
+    _require_cuda(x)
+    t, d = x.shape
+    k = out["idx"].size(1)
+    with torch.cuda.device(x.device):
+        ws = workspace(x.device, t, experts, k)
+        check(lib.moe_pack_scatter(x.data_ptr(), x.element_size(), out["idx"].data_ptr(), t, d, int(experts), k,
+                                   out["counts"].data_ptr(), out["offsets"].data_ptr(), out["packed"].data_ptr(),
+                                   out["row_route"].data_ptr(), out["route_row"].data_ptr(), ws.data_ptr(),
+                                   ws.numel(), _stream()))
+    return out
+
+
+def fused_select(logits: torch.Tensor, x: torch.Tensor, experts: int, top_k: int, out: Optional[tuple] = None):
+    """Select + count + scan + pack from given logits in two launches.
+    Returns (idx, gates, counts, offsets, packed, row_route, route_row); `out` may be the tuple a
+    previous call returned, to reuse its buffers."""
+    _require_cuda(logits, x)
+    if logits.dtype not in _DTYPE_CODE:
+        raise RuntimeError("logits must be fp16/bf16/fp32")
+    logits = logits.contiguous()
+    x = x.contiguous()
+    t, d = x.shape
+    dev = x.device
+    with torch.cuda.device(dev):
+        if out is None:
+            out = (torch.empty((t, top_k), dtype=torch.int32, device=dev),
+                   torch.empty((t, top_k), dtype=torch.float32, device=dev),
+                   torch.empty(experts, dtype=torch.int32, device=dev),
+                   torch.empty(experts + 1, dtype=torch.int32, device=dev),
+                   torch.empty((t * top_k, d), dtype=x.dtype, device=dev),
+                   torch.empty(t * top_k, dtype=torch.int32, device=dev),
+                   torch.empty(t * top_k, dtype=torch.int32, device=dev))
+        idx, gates, counts, offsets, packed, row_route, route_row = out
+        ws = workspace(dev, t, experts, top_k)
+        check(lib.moe_fused_select(logits.data_ptr(), _DTYPE_CODE[logits.dtype], x.data_ptr(), x.element_size(), t, d,
+                                   int(experts), int(top_k), idx.data_ptr(), gates.data_ptr(), counts.data_ptr(),
+                                   offsets.data_ptr(), packed.data_ptr(), row_route.data_ptr(), route_row.data_ptr(),
+                                   ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
 def combine(y: torch.Tensor, gates: torch.Tensor, route_row: torch.Tensor, top_k: int) -> torch.Tensor:
     """out[t] = sum_j gates[t,j] * y[route_row[t*k+j]]."""
     _require_cuda(y, gates, route_row)

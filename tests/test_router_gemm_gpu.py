@@ -113,3 +113,16 @@ def test_route_fused_bf16(ops, t, d, e, k, skew_n, skew_b):
     packed, counts, offsets, row_route, _ = oracle.pack_canonical(x.view(torch.int16).numpy(), ref_idx, e)
     np.testing.assert_array_equal(o["packed"].view(torch.int16).cpu().numpy(), packed)
     np.testing.assert_array_equal(o["offsets"].cpu().numpy(), offsets)
+
+
+def test_pack_scatter_reuses_the_histograms_of_the_route(ops):
+    """moe_pack_scatter after moe_route_fused on the same workspace reproduces the pack into fresh buffers."""
+    x, w = _inputs(2000, 512, 64, 9)
+    xc, wc = x.cuda(), w.cuda()
+    o = ops.route_fused(xc, wc, 2, skew_experts=8, skew_bias=2.0)
+    fresh = dict(o, packed=torch.zeros_like(o["packed"]), counts=torch.zeros_like(o["counts"]),
+                 offsets=torch.zeros_like(o["offsets"]), row_route=torch.zeros_like(o["row_route"]),
+                 route_row=torch.zeros_like(o["route_row"]))
+    ops.pack_scatter(xc, 64, fresh)
+    for key in ("packed", "counts", "offsets", "row_route", "route_row"):
+        assert torch.equal(fresh[key], o[key]), key

@@ -175,3 +175,20 @@ def test_pack_then_combine_round_trip_is_identity(ops):
     # every packed row sits inside its expert's segment
     eid = torch.repeat_interleave(torch.arange(e, device="cuda"), counts.long())
     assert torch.equal(eid, idx.reshape(-1)[row_route.long()].long())
+
+
+@pytest.mark.parametrize("t,d,e,k,dtype", [(4096, 1024, 64, 2, torch.float16), (1000, 72, 48, 3, torch.float32),
+                                           (33, 8, 1000, 8, torch.bfloat16), (9000, 64, 64, 2, torch.float16),
+                                           (1, 16, 2, 1, torch.float16)])
+def test_fused_select_equals_select_then_pack(ops, t, d, e, k, dtype):
+    """moe_fused_select (select + tile histograms in one launch, then scatter) gives exactly what
+    the standalone select followed by the standalone pack gives."""
+    logits = _rand_logits(t, e, dtype, 5 + t + e, ties=True).cuda()
+    x = torch.randn(t, d, generator=torch.Generator().manual_seed(t)).half().cuda()
+    idx, gates, counts, offsets, packed, row_route, route_row = ops.fused_select(logits, x, e, k)
+    idx2, gates2 = ops.topk_select(logits, k)
+    c2, o2, p2, rr2, ir2 = ops.pack(x, idx2, e)
+    assert torch.equal(idx, idx2) and torch.equal(gates, gates2)
+    assert torch.equal(counts, c2) and torch.equal(offsets, o2) and torch.equal(packed, p2)
+    assert torch.equal(row_route, rr2) and torch.equal(route_row, ir2)
+    assert ops.read_status() == 0
