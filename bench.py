@@ -17,7 +17,7 @@ Prints ONE JSON line (rank 0).  Keys beyond the common contract:
   cpu_baseline  the reference's CPU routing path (torch port in oracle/cpu_route.py) on the
                 host cores, a bounded sample of the same workload
   e2e           the same metric through the public API with HOST buffers (pinned), host<->device
-                copies inside the timed region
+                copies of every step inside the timed region, two steps in flight (HostRouter)
 Timing: CUDA events on the launching stream around exactly K steps (captured in one CUDA graph),
 max over ranks; inputs and outputs rotate over several buffer sets whose total size exceeds the
 L2, so every step reads its tokens from HBM.
@@ -256,6 +256,7 @@ def main_ours(args):
     g_select = capture(select_only, steps)
     g_selpack = capture(select_pack, steps)
     ops.route_fused(xs[0], w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B, out=outs[0])  # histograms of set 0
+    torch.cuda.synchronize()
     g_scatter = capture(scatter_only, steps)
     g_route.replay()  # one untimed replay: graph upload
     torch.cuda.synchronize()
@@ -272,14 +273,15 @@ def main_ours(args):
     select_ms = timed(g_select)
     selpack_us = timed(g_selpack) / steps * 1e3
     ops.route_fused(xs[0], w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B, out=outs[0])
+    torch.cuda.synchronize()
     scatter_direct_us = timed(g_scatter) / steps * 1e3
 
     ms_per_step = total_ms / steps
     select_us = select_ms / steps * 1e3
     # Duration of the scatter kernel inside the timed region: fused step minus the router kernel.
-    # (Launched alone back to back it is slower, see `alone_back_to_back_us`: its 67 MB of stores are
-    # absorbed by the L2 and written back to DRAM under the NEXT kernel; with nothing but scatters in
-    # the queue the write-back has no read phase to hide under and write-only HBM bandwidth governs.)
+    # (Launched alone back to back it is ~4 us slower, see `alone_back_to_back_us`: its 67 MB of stores
+    # are absorbed by the L2 and written back to DRAM under the NEXT kernel; with nothing but scatters
+    # in the queue the write-back has no read phase to hide under and write-only HBM bandwidth governs.)
     scatter_us = max(ms_per_step * 1e3 - select_us, 1e-3)
     value = world * T / (ms_per_step * 1e-3)
     peak, peak_kind = measured_peak_gbs()
@@ -287,34 +289,39 @@ def main_ours(args):
     route_gbs = ROUTE_BYTES / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the public API with host buffers -------------------------------
+    # Two slots on two streams: the download of step i overlaps the upload and kernels of step i+1
+    # (separate copy engines); every step still uploads its x and the router weight and downloads all
+    # seven result tensors.  `latency_ms` is one step alone (upload, kernels, download in series).
+    from moe_routers_b200.host import HostRouter
+
     x_host = xs[0].cpu().pin_memory()
-    w_host = w_cpu.pin_memory()
-    host_out = {k: torch.empty(v.shape, dtype=v.dtype).pin_memory() for k, v in outs[0].items()}
-    x_dev, w_dev = torch.empty_like(xs[0]), torch.empty_like(w)
-
-    def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        w_dev.copy_(w_host, non_blocking=True)
-        o = ops.route_fused(x_dev, w_dev, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B, out=outs[0])
-        for k, v in o.items():
-            host_out[k].copy_(v, non_blocking=True)
-        torch.cuda.synchronize()
-
-    e2e_steps = max(3, min(steps, 20))
+    hr = HostRouter(T, D, w_cpu, K_TOP, depth=2, skew_experts=SKEW_N, skew_bias=SKEW_B, device=dev,
+                    upload_weight_each_call=True)
+    e2e_steps = max(4, min(steps, 20))
     for _ in range(3):
-        e2e_step()
-    if world > 1:
-        dist.barrier()
+        hr.route(x_host)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        e2e_step()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+        hr.route(x_host)
+    e2e_latency_s = (time.perf_counter() - t0) / e2e_steps
     if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    prev = hr.submit(x_host)
+    for _ in range(e2e_steps - 1):
+        cur = hr.submit(x_host)
+        hr.result(prev)
+        prev = cur
+    last = hr.result(prev)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    assert int(last["offsets"][-1]) == T * K_TOP  # the downloaded result is a complete route
+    if world > 1:
+        t = torch.tensor([e2e_s, e2e_latency_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    h2d = x_host.numel() * 2 + w_host.numel() * 2
-    d2h = sum(v.numel() * v.element_size() for v in host_out.values())
+        e2e_s, e2e_latency_s = (float(v) for v in t.tolist())
+    h2d, d2h = hr.h2d_bytes, hr.d2h_bytes
+    del hr
 
     # ---- the expert-parallel MoE layer on the same ranks (T=4096 tokens per rank, 64 experts split
     # over the ranks, 2-layer GELU experts 4096 -> 8192 -> 4096), skewed and unskewed -------------
@@ -367,7 +374,8 @@ def main_ours(args):
                 "achieved": (PACK_BYTES + T * E * 2 + T * K_TOP * 4) / (selpack_us * 1e-6) / 1e9, "peak": peak,
                 "unit": "GB/s", "frac": (PACK_BYTES + T * E * 2 + T * K_TOP * 4) / (selpack_us * 1e-6) / 1e9 / peak},
             "e2e": {"value": world * T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "pipeline_depth": 2,
+                    "latency_ms": e2e_latency_s * 1e3},
             "gpu_launches": 2 * steps,
             "clocks": sampler.summary(),
             "ep_layer": ep,

@@ -1,0 +1,85 @@
+"""Route batches whose tokens live in HOST memory.
+
+The reference's operator takes device tensors (kernels/fused_select.cu:203-215); a caller that
+keeps activations on the host pays one upload of `x` and one download of the five results per
+call.  `HostRouter` keeps `depth` slots, each with its own stream, device buffers and pinned host
+result buffers, so that the download of batch i (device -> host copy engine) runs while batch
+i+1 uploads (host -> device copy engine) and routes:
+
+    r = HostRouter(tokens, d_model, w_router_host, top_k=2)
+    t0 = r.submit(x0)            # returns at once; x0 must stay untouched until result(t0)
+    t1 = r.submit(x1)
+    out0 = r.result(t0)          # dict of pinned host tensors: idx, gates, counts, offsets, packed, ...
+
+All compute is the library's route kernels; nothing here falls back to the CPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+class HostRouter:
+    def __init__(self, tokens: int, d_model: int, w_router: torch.Tensor, top_k: int = 2, *, depth: int = 2,
+                 skew_experts: int = 0, skew_bias: float = 0.0, device=None, upload_weight_each_call: bool = False):
+        if depth < 1:
+            raise ValueError("depth must be >= 1")
+        if w_router.dim() != 2 or w_router.size(1) != d_model:
+            raise RuntimeError("w_router shape must be [E, d_model]")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.tokens, self.d, self.k = int(tokens), int(d_model), int(top_k)
+        self.skew = (int(skew_experts), float(skew_bias))
+        self.upload_w = bool(upload_weight_each_call)
+        self.w_host = w_router if w_router.is_pinned() else w_router.contiguous().pin_memory()
+        self.slots = []
+        for _ in range(depth):
+            s = torch.cuda.Stream(device=self.device)
+            x_dev = torch.zeros((tokens, d_model), dtype=w_router.dtype, device=self.device)
+            w_dev = self.w_host.to(self.device)  # one copy per slot: a per-call upload never races another slot
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.stream(s):
+                dev_out = ops.route_fused(x_dev, w_dev, self.k)  # allocates the outputs once
+            host_out = {n: torch.empty(v.shape, dtype=v.dtype).pin_memory() for n, v in dev_out.items() if n != "workspace"}
+            self.slots.append(dict(stream=s, x=x_dev, w=w_dev, dev=dev_out, host=host_out,
+                                   done=torch.cuda.Event(), busy=False))
+        torch.cuda.synchronize(self.device)
+        self._next = 0
+        self.h2d_bytes = tokens * d_model * w_router.element_size() + (self.w_host.numel() * self.w_host.element_size()
+                                                                       if self.upload_w else 0)
+        self.d2h_bytes = sum(v.numel() * v.element_size() for v in self.slots[0]["host"].values())
+
+    def submit(self, x_host: torch.Tensor) -> int:
+        """Queue upload + route + download of one batch; returns the ticket for `result`."""
+        if x_host.is_cuda:
+            raise RuntimeError("x must be a host tensor")
+        if tuple(x_host.shape) != (self.tokens, self.d) or x_host.dtype != self.w_host.dtype:
+            raise RuntimeError("x shape must be [T, d_model] in the router weight's dtype")
+        ticket = self._next
+        slot = self.slots[ticket % len(self.slots)]
+        if slot["busy"]:
+            raise RuntimeError("slot still holds an unread result: call result() on the oldest ticket first")
+        self._next += 1
+        with torch.cuda.stream(slot["stream"]):
+            slot["x"].copy_(x_host, non_blocking=True)
+            if self.upload_w:
+                slot["w"].copy_(self.w_host, non_blocking=True)
+            o = ops.route_fused(slot["x"], slot["w"], self.k, skew_experts=self.skew[0], skew_bias=self.skew[1],
+                                out=slot["dev"])
+            for n, h in slot["host"].items():
+                h.copy_(o[n], non_blocking=True)
+            slot["done"].record(slot["stream"])
+        slot["busy"] = True
+        return ticket
+
+    def result(self, ticket: int) -> dict:
+        """Wait for a ticket; the returned pinned tensors are reused by ticket + depth."""
+        slot = self.slots[ticket % len(self.slots)]
+        if not slot["busy"]:
+            raise RuntimeError("no pending result for this ticket")
+        slot["done"].synchronize()
+        slot["busy"] = False
+        return slot["host"]
+
+    def route(self, x_host: torch.Tensor) -> dict:
+        return self.result(self.submit(x_host))

@@ -100,12 +100,15 @@ def pack(x: torch.Tensor, idx: torch.Tensor, experts: int, *, copy_rows: bool = 
 
 def pack_scatter(x: torch.Tensor, experts: int, out: dict) -> dict:
     """Re-run only the scatter half of `route_fused` into the buffers of `out` (a dict returned by
-    route_fused for the same x): the tile histograms of that call must still be in the workspace."""
+    route_fused for the same x).  The per-tile histograms of that call are read from
+    `out["workspace"]`, the scratch buffer route_fused used (scratch is per stream, so the buffer of
+    the calling stream would be the wrong one after a stream switch); no other route may have run
+    on that buffer in between."""
     _require_cuda(x)
     t, d = x.shape
     k = out["idx"].size(1)
     with torch.cuda.device(x.device):
-        ws = workspace(x.device, t, experts, k)
+        ws = out["workspace"]
         check(lib.moe_pack_scatter(x.data_ptr(), x.element_size(), out["idx"].data_ptr(), t, d, int(experts), k,
                                    out["counts"].data_ptr(), out["offsets"].data_ptr(), out["packed"].data_ptr(),
                                    out["row_route"].data_ptr(), out["route_row"].data_ptr(), ws.data_ptr(),
@@ -187,8 +190,10 @@ def route_fused(x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, skew_exp
     """The whole fused_select strategy: logit GEMM + select + count/scan/pack.
 
     Returns a dict with idx, gates, counts, offsets, packed, row_route,
-    route_row (and logits when asked).  `out` may carry pre-allocated tensors
-    from a previous call to avoid re-allocation.
+    route_row (and logits when asked), plus `workspace`: the scratch buffer
+    of the calling stream, which holds the per-tile histograms of this call
+    until the next route on that stream.  `out` may carry pre-allocated
+    tensors from a previous call to avoid re-allocation.
     """
     _require_cuda(x, w_router)
     if x.dtype not in (torch.float16, torch.bfloat16) or w_router.dtype != x.dtype:
@@ -210,7 +215,7 @@ def route_fused(x: torch.Tensor, w_router: torch.Tensor, top_k: int, *, skew_exp
             o["route_row"] = torch.empty(t * top_k, dtype=torch.int32, device=dev)
         if return_logits and "logits" not in o:
             o["logits"] = torch.empty((t, e), dtype=torch.float32, device=dev)
-        ws = workspace(dev, t, e, top_k)
+        ws = o["workspace"] = workspace(dev, t, e, top_k)
         check(lib.moe_route_fused(x.data_ptr(), w_router.data_ptr(), _DTYPE_CODE[x.dtype], t, d, e, int(top_k),
                                   int(skew_experts), float(skew_bias), o["idx"].data_ptr(),
                                   o["gates"].data_ptr(), o["counts"].data_ptr(), o["offsets"].data_ptr(),

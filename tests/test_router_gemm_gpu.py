@@ -126,3 +126,13 @@ def test_pack_scatter_reuses_the_histograms_of_the_route(ops):
     ops.pack_scatter(xc, 64, fresh)
     for key in ("packed", "counts", "offsets", "row_route", "route_row"):
         assert torch.equal(fresh[key], o[key]), key
+    # from another stream: the histograms are taken from o["workspace"], not from that stream's scratch
+    other = dict(o, packed=torch.zeros_like(o["packed"]), counts=torch.zeros_like(o["counts"]),
+                 offsets=torch.zeros_like(o["offsets"]))
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ops.pack_scatter(xc, 64, other)
+    side.synchronize()
+    for key in ("packed", "counts", "offsets"):
+        assert torch.equal(other[key], o[key]), key
