@@ -221,6 +221,22 @@ int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offse
                      size_t workspace_bytes, void* stream);
 
 /*
+ * moe_grouped_gemm with scattered output rows: row r of the result is stored at c_rows[r] (a device
+ * array of `rows` addresses, each 16-byte aligned with room for N elements) instead of row r of a
+ * dense C.  The addresses may point into another GPU's memory mapped into this process
+ * (moe_ipc_open): the expert-parallel layer passes the table built by moe_ep_row_targets so that the
+ * second expert GEMM returns every result row to the packed slot of the rank it came from, from
+ * inside the GEMM kernel (128-byte row pieces, plain stores).
+ * Replaces, together with moe_ep_row_targets: the per-expert MLP loop followed by a separate return
+ * exchange, which the reference leaves out (bench_2gpu_pcie.py:123-171, :20-25).  All other
+ * arguments as moe_grouped_gemm.
+ */
+int moe_grouped_gemm_rows(const void* a, const void* w, void* const* c_rows, const int32_t* offsets, int experts,
+                          int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
+                          const float* row_scale, const void* bias, int dtype, int sm_margin, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/*
  * Expert-parallel re-bucketing of rows received by the dispatch all-to-all.
  * Replaces: the argsort / index_select / bincount bucketing of received rows
  * (bench_2gpu_pcie.py:130-171) on the owner rank.
@@ -268,6 +284,16 @@ int moe_ipc_close(void* base);
 
 int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts, int world,
                 int rank, int combine, int d, int elem_bytes, int32_t* local_offsets, void* stream);
+
+/*
+ * Return addresses for the combine direction: row_ptrs[i] (i over this rank's expert-major inbox rows,
+ * the order moe_ep_push dispatch produces) = address of the packed slot that row came from, inside
+ * home_bufs[source rank] (device array of `world` base addresses of the ranks' [k*T, d] result
+ * buffers, peers' through their mappings).  Input of moe_grouped_gemm_rows.
+ * Replaces: the bookkeeping of the (missing) return exchange, bench_2gpu_pcie.py:20-25.
+ */
+int moe_ep_row_targets(void* const* home_bufs, const int32_t* counts_all, int experts, int world, int rank,
+                       int d, int elem_bytes, void** row_ptrs, void* stream);
 
 #ifdef __cplusplus
 }

@@ -59,6 +59,7 @@ def run(args) -> list[dict]:
         layer = EPMoELayer(w_router, w1, w2, k, activation="gelu", strategy=strategy,
                            sinkhorn_iters=args.sinkhorn_iters, sinkhorn_temperature=args.sinkhorn_temperature,
                            skew_experts=args.skew_experts, skew_bias=args.skew_bias, transport=transport)
+        layer.fuse_combine = not getattr(args, "no_fuse_combine", False)
         dist.barrier()
         for _ in range(args.warmup):
             layer(x, overlap=True)
@@ -77,14 +78,18 @@ def run(args) -> list[dict]:
                 dist.all_gather_into_tensor(counts_all, o["counts"])
                 y_packed = pr["y_home"]
 
-                def comm():
+                fused = layer.fuse_combine
+                targets = layer._row_targets(counts_all) if fused else None
+
+                def comm():  # with the fused return, the result rows travel inside comp()
                     layer._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
                     layer._rank_sync()
-                    layer._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
+                    if not fused:
+                        layer._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
                     layer._rank_sync()
 
                 def comp():
-                    layer._ffn(pr["inbox"], pr["offsets"], pr["yb"])
+                    layer._ffn(pr["inbox"], pr["offsets"], None if fused else pr["yb"], out_rows=targets)
             else:
                 counts_all, counts_host = layer.exchange_counts(o["counts"])
                 pl = layer.plan(o, counts_all, counts_host, 1)
@@ -121,7 +126,7 @@ def run(args) -> list[dict]:
             eta_overlap=(t_route + t_comm + t_comp + t_combine) / max(t_ovl, 1e-6),
             load_max_over_mean=float(counts.max() / (mean + 1e-9)),
             load_cv=float(counts.std(unbiased=False) / (mean + 1e-9)),
-            transport=transport,
+            transport=transport, fuse_combine=bool(layer.fuse_combine) if transport == "peer" else None,
             rows_received_rank0=int(counts_rk[:, :el].sum()) if rank == 0 else None,
             tokens_per_s=world * t / (t_ovl * 1e-6),
         ))
@@ -148,6 +153,8 @@ def main() -> None:
     p.add_argument("--skew_bias", type=float, default=0.0)
     p.add_argument("--transport", type=str, default="peer", choices=["peer", "nccl"],
                    help="peer: device-initiated stores into the owner's inbox over NVLink; nccl: grouped send/recv")
+    p.add_argument("--no_fuse_combine", action="store_true",
+                   help="peer transport: dense FFN result + a separate return push instead of the GEMM that returns its rows")
     p.add_argument("--json", type=str, default=None, help="also write the results to this file (rank 0)")
     args = p.parse_args()
 

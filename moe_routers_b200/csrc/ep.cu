@@ -194,6 +194,41 @@ ep_push_kernel(const char* __restrict__ local, char* const* __restrict__ peer_bu
   for (; i < n; i += kThreads) d4[i] = __ldg(s4 + i);
 }
 
+
+// Row targets for the combine direction: for every row of this rank's expert-major inbox, the address
+// of the packed slot it came from (in the memory of the rank that sent it).  One CTA per (source rank
+// s, local expert e) segment: inbox rows B_me(s, e) + j  ->  home[s] + (off_s[me*E_local + e] + j) rows.
+// moe_grouped_gemm_rows takes this table so that the second expert GEMM stores its result rows there.
+__global__ void __launch_bounds__(kThreads)
+ep_row_targets_kernel(char* const* __restrict__ home_bufs, const int32_t* __restrict__ counts_all, int experts,
+                      int world, int rank, size_t row_bytes, char** __restrict__ row_ptrs) {
+  __shared__ int s_off, s_b, s_len;
+  const int el = experts / world;
+  const int src = blockIdx.x / el;
+  const int e = blockIdx.x % el;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const int ge = rank * el + e;
+    int off = 0, b = 0;
+    for (int g = lane; g < ge; g += 32) off += counts_all[(size_t)src * experts + g];
+    for (int i = lane; i < world * el; i += 32) {
+      const int ss = i / el, ee = i % el;
+      if (ee < e || (ee == e && ss < src)) b += counts_all[(size_t)ss * experts + rank * el + ee];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      off += __shfl_xor_sync(0xffffffffu, off, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (lane == 0) {
+      s_off = off; s_b = b;
+      s_len = counts_all[(size_t)src * experts + ge];
+    }
+  }
+  __syncthreads();
+  char* base = home_bufs[src] + (size_t)s_off * row_bytes;
+  for (int j = threadIdx.x; j < s_len; j += kThreads) row_ptrs[s_b + j] = base + (size_t)j * row_bytes;
+}
 }  // namespace
 }  // namespace moe
 
@@ -212,6 +247,21 @@ extern "C" int moe_ep_push(const void* local, void* const* peer_bufs, const int3
       static_cast<const char*>(local), reinterpret_cast<char* const*>(peer_bufs), counts_all, experts, world, rank,
       combine ? 1 : 0, (size_t)d * elem_bytes, local_offsets);
   return check_launch("ep_push_kernel");
+}
+
+extern "C" int moe_ep_row_targets(void* const* home_bufs, const int32_t* counts_all, int experts, int world, int rank,
+                                  int d, int elem_bytes, void** row_ptrs, void* stream) {
+  using namespace moe;
+  if (experts <= 0 || world <= 0 || experts % world != 0)
+    return fail(MOE_ERR_ARG, "experts must be divisible by world_size");
+  if (rank < 0 || rank >= world) return fail(MOE_ERR_ARG, "moe_ep_row_targets: bad rank");
+  if (d <= 0 || (elem_bytes != 2 && elem_bytes != 4) || ((size_t)d * elem_bytes) % 16 != 0)
+    return fail(MOE_ERR_ARG, "moe_ep_row_targets: rows must be a multiple of 16 bytes");
+  if (!home_bufs || !counts_all || !row_ptrs) return fail(MOE_ERR_ARG, "moe_ep_row_targets: null pointer");
+  ep_row_targets_kernel<<<experts, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<char* const*>(home_bufs), counts_all, experts, world, rank, (size_t)d * elem_bytes,
+      reinterpret_cast<char**>(row_ptrs));
+  return check_launch("ep_row_targets_kernel");
 }
 
 extern "C" int moe_enable_peer_access(int peer_device) {

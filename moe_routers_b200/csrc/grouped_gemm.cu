@@ -16,6 +16,14 @@
 // the expert's segment masked) overlaps the main loop of tile i+1.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4)..).
+//
+// Scattered output (`c_rows`): instead of row r of a dense C, every output row goes to its own base
+// address, which may lie in another GPU's memory (a peer mapping).  The expert-parallel layer uses
+// this for the combine direction: the second expert GEMM stores each result row straight into the
+// packed slot of the rank the row came from, over NVLink, from the same kernel that computes it
+// (plain 128-bit stores; no TMA and no multicast on peer memory).  The epilogue warp stages 32 rows
+// x 64 columns in shared memory and stores them as 128-byte row pieces, 4 rows per instruction,
+// so that a peer store is a full 128-byte write, not 32 scattered 16-byte ones.
 #include "sm100.cuh"
 
 namespace moe {
@@ -40,8 +48,12 @@ struct GParams {
   const uint16_t* bias;  // [experts, n_w] in the data type, or null
   int bf16;              // 0: fp16 data, 1: bf16 data
   uint16_t* c;
+  uint16_t* const* c_rows;  // null: dense C; else base address of every output row
   int32_t* status;
 };
+
+constexpr int kStageRowBytes = 144;               // 64 columns x 2 B + 16 B pad: conflict-free both ways
+constexpr int kStageWarpBytes = 32 * kStageRowBytes;
 
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
@@ -120,6 +132,21 @@ __device__ __forceinline__ void epilogue_chunk(uint32_t t_main, uint32_t t_up, b
   }
 }
 
+// Store 32 staged rows x 64 columns (one epilogue warp's staging area, filled by epilogue_chunk with
+// dst_h pointing into it) to the rows' own base addresses: lane l handles the 16-byte piece l%8 of
+// row 4*i + l/8 in pass i.  `my_row` / `my_valid` describe the row this lane owns (row == lane).
+__device__ __forceinline__ void store_staged_rows(const uint8_t* stage, uint16_t* my_row, bool my_valid, int col0,
+                                                  int lane) {
+  const unsigned long long mine = my_valid ? reinterpret_cast<unsigned long long>(my_row) : 0ull;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = 4 * i + (lane >> 3);
+    const unsigned long long base = __shfl_sync(0xffffffffu, mine, r);
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * kStageRowBytes + (lane & 7) * 16);
+    if (base != 0ull) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + col0 + (lane & 7) * 8) = v;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const GParams p) {
@@ -136,6 +163,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   // full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2]
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);
   int32_t* s_mt = reinterpret_cast<int32_t*>(s_tmem + 4);  // [experts + 1]
+  // staging for scattered output rows: 4 epilogue warps x 32 rows x 144 B, 16-byte aligned
+  uint8_t* s_stage = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(s_mt + p.experts + 1) + 15) & ~static_cast<uintptr_t>(15));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -277,11 +307,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
       const float scale = (valid && p.row_scale != nullptr) ? p.row_scale[grow] : 1.f;
-      uint16_t* crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
+      uint16_t* crow;
+      if (p.c_rows == nullptr) crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
+      else crow = (valid ? p.c_rows[grow] : nullptr) + (size_t)nt * out_bn;
       // bias of expert e: main columns at nt*out_bn, SwiGLU up columns n_out further
       const int n_w = swiglu ? 2 * p.n_out : p.n_out;
       const uint16_t* brow = p.bias ? p.bias + (size_t)e * n_w + (size_t)nt * out_bn : nullptr;
-      if (out_bn % 32 == 0) {
+      if (p.c_rows != nullptr && out_bn % 64 == 0) {
+        uint8_t* stage = s_stage + q * kStageWarpBytes;
+        uint16_t* mine = reinterpret_cast<uint16_t*>(stage + lane * kStageRowBytes);
+        for (int c0 = 0; c0 < out_bn; c0 += 64) {
+#pragma unroll
+          for (int h = 0; h < 64; h += 32)
+            epilogue_chunk<32>(acc + (uint32_t)(c0 + h), acc + (uint32_t)(out_bn + c0 + h), swiglu, p.act, scale, true,
+                               mine + h, brow ? brow + c0 + h : nullptr,
+                               (brow && swiglu) ? brow + p.n_out + c0 + h : nullptr, p.bf16 != 0);
+          __syncwarp();
+          store_staged_rows(stage, crow, valid, c0, lane);
+          __syncwarp();
+        }
+      } else if (out_bn % 32 == 0) {
         for (int c0 = 0; c0 < out_bn; c0 += 32)
           epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0,
                              brow ? brow + c0 : nullptr, (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
@@ -306,11 +351,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 }  // namespace
 }  // namespace moe
 
-extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts, int rows,
-                                int K, int N, int w_layout, int64_t stride_w, int activation,
-                                const float* row_scale, const void* bias, int dtype, int sm_margin,
-                                void* workspace, size_t workspace_bytes, void* stream) {
-  using namespace moe;
+namespace moe {
+namespace {
+int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_rows, const int32_t* offsets,
+                        int experts, int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
+                        const float* row_scale, const void* bias, int dtype, int sm_margin, void* workspace,
+                        size_t workspace_bytes, void* stream) {
   if (experts <= 0 || rows < 0 || K <= 0 || N <= 0) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad shape");
   if (experts > kMaxExperts) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: experts must be <= %d", kMaxExperts);
   if (K % 8 != 0) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: K must be a multiple of 8, got %d", K);
@@ -321,7 +367,7 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   if (w_layout != MOE_W_KN && w_layout != MOE_W_NK) return fail(MOE_ERR_ARG, "moe_grouped_gemm: bad weight layout");
   if (dtype != MOE_F16 && dtype != MOE_BF16) return fail(MOE_ERR_ARG, "moe_grouped_gemm: dtype must be fp16 or bf16");
   if (rows == 0) return MOE_OK;
-  if (!a || !w || !c || !offsets) return fail(MOE_ERR_ARG, "moe_grouped_gemm: null pointer");
+  if (!a || !w || (!c && !c_rows) || !offsets) return fail(MOE_ERR_ARG, "moe_grouped_gemm: null pointer");
   if (!workspace || workspace_bytes < (size_t)kStatusBytes) return fail(MOE_ERR_WORKSPACE, "moe_grouped_gemm: workspace missing");
   const bool swiglu = activation == MOE_ACT_SWIGLU;
   const int n_w = swiglu ? 2 * N : N;  // output features held by one weight matrix
@@ -338,6 +384,7 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   p.act = activation;
   p.row_scale = row_scale;
   p.c = static_cast<uint16_t*>(c);
+  p.c_rows = reinterpret_cast<uint16_t* const*>(c_rows);
   p.bias = static_cast<const uint16_t*>(bias);
   p.bf16 = dtype == MOE_BF16;
   p.status = static_cast<int32_t*>(workspace);
@@ -356,7 +403,7 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   if (rc != MOE_OK) return rc;
 
   const int stage_bytes = kABytes + p.bn * kBK * 2;
-  const int fixed = (2 * kMaxStages + 4) * 8 + 16 + (experts + 1) * 4 + 64;
+  const int fixed = (2 * kMaxStages + 4) * 8 + 16 + (experts + 1) * 4 + 64 + (c_rows ? 4 * kStageWarpBytes + 16 : 0);
   int stages = (227 * 1024 - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return fail(MOE_ERR_UNSUPPORTED, "moe_grouped_gemm: shared memory budget exceeded");
@@ -376,4 +423,23 @@ extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int
   if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_grouped_gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   grouped_gemm_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tmap_a, tmap_w, p);
   return check_launch("grouped_gemm_kernel");
+}
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_grouped_gemm(const void* a, const void* w, void* c, const int32_t* offsets, int experts, int rows,
+                                int K, int N, int w_layout, int64_t stride_w, int activation,
+                                const float* row_scale, const void* bias, int dtype, int sm_margin,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  return moe::grouped_gemm_launch(a, w, c, nullptr, offsets, experts, rows, K, N, w_layout, stride_w, activation,
+                                  row_scale, bias, dtype, sm_margin, workspace, workspace_bytes, stream);
+}
+
+extern "C" int moe_grouped_gemm_rows(const void* a, const void* w, void* const* c_rows, const int32_t* offsets,
+                                     int experts, int rows, int K, int N, int w_layout, int64_t stride_w,
+                                     int activation, const float* row_scale, const void* bias, int dtype,
+                                     int sm_margin, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!c_rows) return moe::fail(MOE_ERR_ARG, "moe_grouped_gemm_rows: null row table");
+  return moe::grouped_gemm_launch(a, w, nullptr, c_rows, offsets, experts, rows, K, N, w_layout, stride_w, activation,
+                                  row_scale, bias, dtype, sm_margin, workspace, workspace_bytes, stream);
 }

@@ -108,6 +108,9 @@ class EPMoELayer:
         # inbox over NVLink (CUDA IPC mappings), no host synchronisation in the layer.
         # "nccl": grouped NCCL send/recv plus re-bucketing on the owner.
         self.transport = transport
+        # peer transport: the second expert GEMM stores its result rows straight into the home ranks'
+        # packed slots (one kernel computes and returns); False: dense result + a separate push
+        self.fuse_combine = True
         self._peer = None
         self.comm_stream = torch.cuda.Stream()
         # Expert groups pipelined against the exchanges, and SMs the persistent GEMM leaves to the
@@ -138,11 +141,14 @@ class EPMoELayer:
         dist.all_gather_into_tensor(all_counts, counts, group=self.group)
         return all_counts, all_counts.cpu()
 
-    def _ffn(self, rows, offsets, out, e_lo=0, e_cnt=None, sm_margin=0):
+    def _ffn(self, rows, offsets, out, e_lo=0, e_cnt=None, sm_margin=0, out_rows=None):
+        """Both expert GEMMs; with `out_rows` the second one stores every result row at its own
+        address (the packed slot of the rank it came from) instead of into `out`."""
         e_hi = self.el if e_cnt is None else e_lo + e_cnt
         h = ops.grouped_gemm(rows, self.w1[e_lo:e_hi], offsets, layout="nk", activation=self.activation,
                              sm_margin=sm_margin)
-        return ops.grouped_gemm(h, self.w2[e_lo:e_hi], offsets, layout="nk", out=out, sm_margin=sm_margin)
+        return ops.grouped_gemm(h, self.w2[e_lo:e_hi], offsets, layout="nk", out=out, sm_margin=sm_margin,
+                                out_rows=out_rows)
 
     def _rebucket(self, src, dst, counts_all, backward, local_offsets, e_lo, e_cnt):
         check(lib.moe_ep_rebucket(src.data_ptr(), dst.data_ptr(), counts_all.data_ptr(), self.e, self.world,
@@ -264,6 +270,7 @@ class EPMoELayer:
             inbox_ptrs=torch.tensor(in_ptrs, dtype=torch.int64, device=device),
             home_ptrs=torch.tensor(home_ptrs, dtype=torch.int64, device=device),
             yb=torch.empty((cap, d), dtype=dtype, device=device),
+            targets=torch.zeros(cap, dtype=torch.int64, device=device),
             offsets=torch.zeros(self.el + 1, dtype=torch.int32, device=device),
             flag=torch.zeros(1, dtype=torch.int32, device=device),
         )
@@ -283,6 +290,13 @@ class EPMoELayer:
                               local_offsets.data_ptr() if local_offsets is not None else None,
                               torch.cuda.current_stream().cuda_stream))
 
+    def _row_targets(self, counts_all):
+        pr = self._peer
+        check(lib.moe_ep_row_targets(pr["home_ptrs"].data_ptr(), counts_all.data_ptr(), self.e, self.world, self.rank,
+                                     pr["d"], pr["inbox"].element_size(), pr["targets"].data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream))
+        return pr["targets"]
+
     def _rank_sync(self):
         """Order the phases across ranks on the stream: a one-element all-reduce (no host wait)."""
         dist.all_reduce(self._peer["flag"], group=self.group)
@@ -299,9 +313,14 @@ class EPMoELayer:
         # every rank has left the previous call's combine before anybody overwrites an inbox: the
         # all-gather above is that barrier (it completes only when every rank has reached it)
         self._push(packed, pr["inbox_ptrs"], counts_all, False, pr["offsets"])
-        self._rank_sync()  # all rows have arrived in every inbox
-        self._ffn(pr["inbox"], pr["offsets"], pr["yb"])
-        self._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
+        if self.fuse_combine:
+            targets = self._row_targets(counts_all)
+            self._rank_sync()  # all rows have arrived in every inbox
+            self._ffn(pr["inbox"], pr["offsets"], None, out_rows=targets)  # computes and returns the rows
+        else:
+            self._rank_sync()
+            self._ffn(pr["inbox"], pr["offsets"], pr["yb"])
+            self._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
         self._rank_sync()  # all results are back in their home slots
         out = ops.combine(pr["y_home"], o["gates"], o["route_row"], self.k)
         self.last = dict(counts_dev=counts_all, route=o)

@@ -254,13 +254,16 @@ _ACT = {None: _lib.MOE_ACT_NONE, "none": _lib.MOE_ACT_NONE, "gelu": _lib.MOE_ACT
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, layout: str = "nk",
                  activation: Optional[str] = None, row_scale: Optional[torch.Tensor] = None,
                  out: Optional[torch.Tensor] = None, sm_margin: int = 0,
-                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 bias: Optional[torch.Tensor] = None, out_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """c[offsets[e]:offsets[e+1]] = act(a[offsets[e]:offsets[e+1]] @ W[e]) for every expert.
 
     a [rows, K]; w [E, N, K] (layout "nk") or [E, K, N] (layout "kn"); both fp16 or both bf16;
     offsets int32 [E+1] on the device; bias [E, output features] (same dtype) is added before the
     activation.  With activation "swiglu" the weight has
     2N output features (gate rows first, then up) and the result has N columns.
+    With `out_rows` (int64 [rows] on the device: one 16-byte aligned address per result row, possibly
+    in a mapped peer buffer) the rows are stored there instead of in a dense result, and the table
+    itself is returned.
     """
     _require_cuda(a, w, offsets)
     if a.dtype not in (torch.float16, torch.bfloat16) or w.dtype != a.dtype:
@@ -281,9 +284,20 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, lay
     n_out = n_w // 2 if act == _lib.MOE_ACT_SWIGLU else n_w
     dev = a.device
     with torch.cuda.device(dev):
-        c = out if out is not None else torch.empty((rows, n_out), dtype=a.dtype, device=dev)
         ws = workspace(dev, 1, e, 1)
         rs = row_scale.to(torch.float32).contiguous() if row_scale is not None else None
+        if out_rows is not None:
+            if out_rows.dtype != torch.int64 or not out_rows.is_cuda or out_rows.numel() < rows:
+                raise RuntimeError("grouped_gemm: out_rows must be a CUDA int64 tensor with one address per row")
+            check(lib.moe_grouped_gemm_rows(a.data_ptr(), w.data_ptr(), out_rows.data_ptr(), offsets.data_ptr(), e,
+                                            rows, k_dim, n_out,
+                                            _lib.MOE_W_NK if layout == "nk" else _lib.MOE_W_KN, w.stride(0), act,
+                                            rs.data_ptr() if rs is not None else None,
+                                            bias.contiguous().data_ptr() if bias is not None else None,
+                                            _DTYPE_CODE[a.dtype], int(sm_margin), ws.data_ptr(), ws.numel(),
+                                            _stream()))
+            return out_rows
+        c = out if out is not None else torch.empty((rows, n_out), dtype=a.dtype, device=dev)
         check(lib.moe_grouped_gemm(a.data_ptr(), w.data_ptr(), c.data_ptr(), offsets.data_ptr(), e, rows,
                                    k_dim, n_out, _lib.MOE_W_NK if layout == "nk" else _lib.MOE_W_KN,
                                    w.stride(0), act, rs.data_ptr() if rs is not None else None,

@@ -103,6 +103,52 @@ def test_push_kernel_emulated_ranks(world, e, d):
         np.testing.assert_array_equal(home[r].cpu().numpy()[:n], packed[r].cpu().numpy()[:n])
 
 
+@pytest.mark.parametrize("world,e,d", [(4, 16, 64), (2, 8, 128), (8, 64, 256), (1, 4, 64)])
+def test_row_targets_and_gemm_return_emulated_ranks(world, e, d):
+    """Combine direction fused into the expert GEMM, all ranks emulated on one GPU: the row-target
+    table must send inbox row i to the packed slot it came from (checked against moe_ep_push in
+    combine mode), and moe_grouped_gemm_rows through that table must leave in every home buffer
+    exactly what the dense GEMM followed by the combine push leaves."""
+    _need_cuda()
+    from moe_routers_b200 import _lib, ops
+
+    el = e // world
+    rng = np.random.default_rng(3 * world + e)
+    counts_all = rng.integers(0, 70, size=(world, e)).astype(np.int32)
+    if world > 1:
+        counts_all[rng.integers(0, world), rng.integers(0, e)] = 0
+    c_t = torch.from_numpy(counts_all).cuda()
+    n_home = [int(counts_all[r].sum()) for r in range(world)]
+    n_in = [int(counts_all[:, r * el:(r + 1) * el].sum()) for r in range(world)]
+    inbox = [torch.from_numpy(rng.standard_normal((n_in[r] + 1, d)).astype(np.float16)).cuda() for r in range(world)]
+    w = [torch.from_numpy((rng.standard_normal((el, d, d)) / d ** 0.5).astype(np.float16)).cuda() for _ in range(world)]
+    home_a = [torch.zeros((n_home[r] + 1, d), dtype=torch.float16, device="cuda") for r in range(world)]
+    home_b = [torch.zeros_like(t) for t in home_a]
+    ptr_a = torch.tensor([t.data_ptr() for t in home_a], dtype=torch.int64, device="cuda")
+    ptr_b = torch.tensor([t.data_ptr() for t in home_b], dtype=torch.int64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for r in range(world):
+        off = np.concatenate([[0], np.cumsum(counts_all[:, r * el:(r + 1) * el].sum(axis=0))]).astype(np.int32)
+        off_t = torch.from_numpy(off).cuda()
+        # path A: dense GEMM, then the combine push
+        y = ops.grouped_gemm(inbox[r][:n_in[r]], w[r], off_t, layout="nk")
+        if n_in[r]:
+            _lib.check(_lib.lib.moe_ep_push(y.data_ptr(), ptr_a.data_ptr(), c_t.data_ptr(), e, world, r, 1, d, 2,
+                                            None, st))
+        # path B: row targets, then the GEMM storing through them
+        table = torch.zeros(n_in[r] + 1, dtype=torch.int64, device="cuda")
+        _lib.check(_lib.lib.moe_ep_row_targets(ptr_b.data_ptr(), c_t.data_ptr(), e, world, r, d, 2,
+                                               table.data_ptr(), st))
+        assert int(table[n_in[r]]) == 0  # nothing written past the last inbox row
+        if n_in[r]:
+            ops.grouped_gemm(inbox[r][:n_in[r]], w[r], off_t, layout="nk", out_rows=table)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    for r in range(world):
+        assert torch.equal(home_a[r], home_b[r])
+        assert home_a[r][:n_home[r]].abs().sum() > 0 or n_home[r] == 0
+
+
 def _ep_worker(rank, world, port, strategy, q):
     try:
         import torch.distributed as dist
@@ -124,10 +170,15 @@ def _ep_worker(rank, world, port, strategy, q):
                                  w2[rank * el:(rank + 1) * el].cuda().contiguous(), k, activation="gelu",
                                  strategy=strategy, skew_experts=4, skew_bias=2.0, transport=tr)
                   for tr in ("peer", "nccl")}
-        for tr, overlap in (("peer", True), ("peer", True), ("nccl", True), ("nccl", False)):
+        outs = {}
+        for tr, overlap, fuse in (("peer", True, True), ("peer", True, True), ("peer", True, False),
+                                  ("nccl", True, None), ("nccl", False, None)):
             layer = layers[tr]
+            if fuse is not None:
+                layer.fuse_combine = fuse  # second GEMM returns its rows itself / dense result + push
             out = layer(x.cuda(), overlap=overlap)
             torch.cuda.synchronize()
+            outs[(tr, fuse)] = out.clone()
             o = layer.last["route"]
             experts = {"w1": w1.numpy(), "w2": w2.numpy()}
             ref, _ = oracle.moe_layer(x.numpy(), o["idx"].cpu().numpy(), o["gates"].cpu().numpy(), experts,
@@ -136,6 +187,8 @@ def _ep_worker(rank, world, port, strategy, q):
             scale = np.abs(ref).max()
             # layer outputs: 2e-2 relative to the output scale (fp16)
             np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2 * scale)
+        # the same kernels did the arithmetic in both peer variants: identical bits
+        assert torch.equal(outs[("peer", True)], outs[("peer", False)])
         dist.barrier()
         for layer in layers.values():
             layer.close()

@@ -175,3 +175,34 @@ def test_demo_pipeline_on_device(ops):
             hh = torch.nn.functional.silu(pk[lo:hi] @ w1[ex].float() + b1[ex].float()).half().float()
             ref[lo:hi] = hh @ w2[ex].float() + b2[ex].float()
     torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("N,act,dtype,bias", [(512, None, torch.float16, False), (256, "gelu", torch.float16, True),
+                                              (128, "swiglu", torch.bfloat16, False), (64, None, torch.float16, False),
+                                              (48, "silu", torch.float16, True), (1024, "swiglu", torch.float16, True)])
+def test_grouped_gemm_scattered_rows_equal_dense(ops, N, act, dtype, bias):
+    """`out_rows`: every result row stored at its own address.  With the addresses of a permuted
+    buffer the result must be the dense result, row-permuted, bit for bit (same kernel arithmetic);
+    rows that no address points to stay untouched."""
+    counts = [130, 0, 257, 1, 64, 300]
+    K = 192
+    off = _segments(counts)
+    rows, e = int(off[-1]), len(counts)
+    g = torch.Generator().manual_seed(N)
+    a = torch.randn(rows, K, generator=g).to(dtype).cuda()
+    n_w = 2 * N if act == "swiglu" else N
+    w = (torch.randn(e, n_w, K, generator=g) / K ** 0.5).to(dtype).cuda()
+    b = (torch.randn(e, n_w, generator=g)).to(dtype).cuda() if bias else None
+    off_t = torch.from_numpy(off).cuda()
+    dense = ops.grouped_gemm(a, w, off_t, layout="nk", activation=act, bias=b)
+    perm = torch.randperm(rows + 7, generator=g)[:rows]  # 7 slots of the target stay unused
+    target = torch.full((rows + 7, N), 7.0, dtype=dtype, device="cuda")
+    table = (target.data_ptr() + perm.to(torch.int64) * (N * 2)).cuda()
+    ops.grouped_gemm(a, w, off_t, layout="nk", activation=act, bias=b, out_rows=table)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    got = target.cpu()
+    assert torch.equal(got[perm].view(torch.int16), dense.cpu().view(torch.int16))
+    unused = torch.ones(rows + 7, dtype=torch.bool)
+    unused[perm] = False
+    assert (got[unused].float() == 7.0).all()
