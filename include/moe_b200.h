@@ -121,6 +121,19 @@ int moe_pack_scatter(const void* x, int elem_bytes, const int32_t* idx, int toke
                      int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * moe_pack_scatter with one destination segment per expert: the rows routed to expert e are stored in
+ * canonical order from seg_base[e] on (device array of `experts` 16-byte aligned addresses, which
+ * may lie in peers' memory) instead of at packed[offsets[e]]; counts, offsets and the maps are
+ * written as by moe_pack.  Rows must be a multiple of 16 bytes.  With the table of
+ * moe_ep_segment_bases this is the dispatch of the expert-parallel layer: the pack writes every row
+ * straight into the owner's inbox over NVLink (bulk stores), replacing pack + all_to_all_single
+ * (bench_2gpu_pcie.py:305-372, :466-494).
+ */
+int moe_pack_scatter_to(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+                        int top_k, int32_t* counts, int32_t* offsets, void* const* seg_base, int32_t* row_route,
+                        int32_t* route_row, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * moe_pack for callers that cannot allocate.  (No counterpart in the reference.)
  * Same inputs, outputs and ordering as moe_pack, but the scratch that moe_pack takes from a
  * caller-owned workspace comes from a 256 KiB array built into the library image, so the call
@@ -284,6 +297,16 @@ int moe_ipc_close(void* base);
 
 int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts, int world,
                 int rank, int combine, int d, int elem_bytes, int32_t* local_offsets, void* stream);
+
+/*
+ * Dispatch destinations: seg_base[g] (g = global expert) = address, inside inbox_bufs[owner of g]
+ * (device array of `world` inbox base addresses, peers' through their mappings), of the first row
+ * this rank contributes to expert g in the owner's expert-major inbox; also writes this rank's own
+ * local_offsets int32 [experts/world + 1] (may be NULL).  Input of moe_pack_scatter_to.
+ * Replaces: the send-split bookkeeping of route_and_pack (bench_2gpu_pcie.py:305-372).
+ */
+int moe_ep_segment_bases(void* const* inbox_bufs, const int32_t* counts_all, int experts, int world, int rank,
+                         int d, int elem_bytes, void** seg_base, int32_t* local_offsets, void* stream);
 
 /*
  * Return addresses for the combine direction: row_ptrs[i] (i over this rank's expert-major inbox rows,

@@ -43,6 +43,8 @@ SIGNATURES = {
     "moe_sinkhorn": (_i, [_p, _i, _i, _i, _i, _i, _f, _f, _p, _p, _p, _sz, _p]),
     "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),
     "moe_grouped_gemm_rows": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),
+    "moe_pack_scatter_to": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "moe_ep_segment_bases": (_i, [_p, _p, _i, _i, _i, _i, _i, _p, _p, _p]),
     "moe_ep_row_targets": (_i, [_p, _p, _i, _i, _i, _i, _i, _p, _p]),
 }
 

@@ -7,11 +7,13 @@ reference leaves out:
     torchrun --nproc_per_node W -m moe_routers_b200.bench_ep --all_strategies --skew_experts 8 --skew_bias 2.0
 
 Per strategy, per iteration (forward only), times in microseconds, max over ranks:
-    T_route      route (logit GEMM + select + pack), one fused call
+    T_route      route (logit GEMM + select + pack), one fused call; with the direct dispatch the rows
+                 are copied by the dispatch itself (T_comm) and T_route is GEMM + select + pack plan
     T_comm       dispatch + combine exchanges, run alone
     T_comp       expert FFN on own rows + on received rows (with re-bucketing), run alone
     T_layer(seq) the whole layer with every stage on one stream
     T_layer(ovl) the whole layer with the exchanges on a second stream
+    T_layer(b2b) the layer called `iters` times back to back, per call (no host sync in between)
     eta_overlap  (T_route + T_comm + T_comp + T_combine) / T_layer(ovl)      (bench_2gpu_pcie.py:586)
     load max/mean and CV of the per-expert route counts over all ranks       (:446-457)
 Each expert is a 2-layer GELU FFN d_model -> hidden -> d_model with N(0, 1/fan_in) weights.
@@ -60,6 +62,7 @@ def run(args) -> list[dict]:
                            sinkhorn_iters=args.sinkhorn_iters, sinkhorn_temperature=args.sinkhorn_temperature,
                            skew_experts=args.skew_experts, skew_bias=args.skew_bias, transport=transport)
         layer.fuse_combine = not getattr(args, "no_fuse_combine", False)
+        layer.direct_dispatch = not getattr(args, "no_direct_dispatch", False)
         dist.barrier()
         for _ in range(args.warmup):
             layer(x, overlap=True)
@@ -70,7 +73,8 @@ def run(args) -> list[dict]:
         acc = dict(route=0.0, comm=0.0, comp=0.0, combine=0.0, seq=0.0, ovl=0.0)
         for _ in range(args.iters):
             out = {}
-            acc["route"] += _event_us(lambda: out.update(o=layer.route(x)))
+            direct = transport == "peer" and layer.direct_dispatch
+            acc["route"] += _event_us(lambda: out.update(o=layer.route_select(x) if direct else layer.route(x)))
             o = out["o"]
             if transport == "peer":
                 pr = layer._peer
@@ -82,7 +86,10 @@ def run(args) -> list[dict]:
                 targets = layer._row_targets(counts_all) if fused else None
 
                 def comm():  # with the fused return, the result rows travel inside comp()
-                    layer._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
+                    if direct:
+                        layer.dispatch_direct(x, o, counts_all)
+                    else:
+                        layer._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
                     layer._rank_sync()
                     if not fused:
                         layer._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
@@ -110,10 +117,15 @@ def run(args) -> list[dict]:
             acc["seq"] += _event_us(lambda: layer(x, overlap=False))
             dist.barrier()
             acc["ovl"] += _event_us(lambda: layer(x, overlap=True))
-        vals = torch.tensor([acc[n] / args.iters for n in ("route", "comm", "comp", "combine", "seq", "ovl")],
+        # the layer called back to back (one event pair around all calls, no host synchronisation in
+        # between): the host's launch work hides behind the previous call's expert GEMMs, as it does
+        # inside a multi-layer model
+        dist.barrier()
+        acc["b2b"] = _event_us(lambda: [layer(x, overlap=True) for _ in range(args.iters)])
+        vals = torch.tensor([acc[n] / args.iters for n in ("route", "comm", "comp", "combine", "seq", "ovl", "b2b")],
                             device=dev, dtype=torch.float64)
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-        t_route, t_comm, t_comp, t_combine, t_seq, t_ovl = [float(v) for v in vals.tolist()]
+        t_route, t_comm, t_comp, t_combine, t_seq, t_ovl, t_b2b = [float(v) for v in vals.tolist()]
 
         counts_rk = layer.last["counts_all"] if "counts_all" in layer.last else layer.last["counts_dev"].cpu()
         counts = counts_rk.sum(dim=0).to(torch.float32)  # aggregated over ranks
@@ -122,13 +134,14 @@ def run(args) -> list[dict]:
             strategy=strategy, world=world, tokens_per_rank=t, d_model=d, hidden=h, experts=e, top_k=k,
             skew_experts=args.skew_experts, skew_bias=args.skew_bias,
             t_route_us=t_route, t_comm_us=t_comm, t_comp_us=t_comp, t_combine_us=t_combine,
-            t_layer_seq_us=t_seq, t_layer_overlap_us=t_ovl,
+            t_layer_seq_us=t_seq, t_layer_overlap_us=t_ovl, t_layer_back_to_back_us=t_b2b,
             eta_overlap=(t_route + t_comm + t_comp + t_combine) / max(t_ovl, 1e-6),
             load_max_over_mean=float(counts.max() / (mean + 1e-9)),
             load_cv=float(counts.std(unbiased=False) / (mean + 1e-9)),
-            transport=transport, fuse_combine=bool(layer.fuse_combine) if transport == "peer" else None,
+            transport=transport, direct_dispatch=bool(layer.direct_dispatch) if transport == "peer" else None,
+            fuse_combine=bool(layer.fuse_combine) if transport == "peer" else None,
             rows_received_rank0=int(counts_rk[:, :el].sum()) if rank == 0 else None,
-            tokens_per_s=world * t / (t_ovl * 1e-6),
+            tokens_per_s=world * t / (t_ovl * 1e-6), tokens_per_s_back_to_back=world * t / (t_b2b * 1e-6),
         ))
         layer.close()
     return results
@@ -155,6 +168,8 @@ def main() -> None:
                    help="peer: device-initiated stores into the owner's inbox over NVLink; nccl: grouped send/recv")
     p.add_argument("--no_fuse_combine", action="store_true",
                    help="peer transport: dense FFN result + a separate return push instead of the GEMM that returns its rows")
+    p.add_argument("--no_direct_dispatch", action="store_true",
+                   help="peer transport: pack locally and push, instead of the pack that stores into the owners' inboxes")
     p.add_argument("--json", type=str, default=None, help="also write the results to this file (rank 0)")
     args = p.parse_args()
 
@@ -170,6 +185,7 @@ def main() -> None:
             for r in results:
                 print(f"{r['strategy']:<13}{r['t_route_us']:9.1f}{r['t_comm_us']:9.1f}{r['t_comp_us']:10.1f}"
                       f"{r['t_combine_us']:8.1f}{r['t_layer_seq_us']:10.1f}{r['t_layer_overlap_us']:10.1f}"
+                      f"{r['t_layer_back_to_back_us']:10.1f}"
                       f"{r['eta_overlap']:6.2f}{r['load_max_over_mean']:9.2f}{r['load_cv']:6.2f}")
             for r in results:
                 print(json.dumps(r))

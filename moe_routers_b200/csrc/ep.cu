@@ -229,6 +229,40 @@ ep_row_targets_kernel(char* const* __restrict__ home_bufs, const int32_t* __rest
   char* base = home_bufs[src] + (size_t)s_off * row_bytes;
   for (int j = threadIdx.x; j < s_len; j += kThreads) row_ptrs[s_b + j] = base + (size_t)j * row_bytes;
 }
+
+// Dispatch destinations for moe_pack_scatter_to: the rows this rank routes to global expert g =
+// p * E_local + e start at row B_p(me, e) of rank p's expert-major inbox.  One CTA per expert; the
+// CTAs of this rank's own experts also write its local_offsets (as the dispatch push does).
+__global__ void __launch_bounds__(32)
+ep_segment_bases_kernel(char* const* __restrict__ inbox_bufs, const int32_t* __restrict__ counts_all, int experts,
+                        int world, int rank, size_t row_bytes, char** __restrict__ seg_base,
+                        int32_t* __restrict__ local_offsets) {
+  const int el = experts / world;
+  const int owner = blockIdx.x / el;
+  const int e = blockIdx.x % el;
+  const int lane = threadIdx.x;
+  int b = 0, first = 0, total = 0;
+  for (int i = lane; i < world * el; i += 32) {
+    const int ss = i / el, ee = i % el;
+    const int l = counts_all[(size_t)ss * experts + owner * el + ee];
+    if (ee < e || (ee == e && ss < rank)) b += l;
+    if (ee < e) first += l;
+    total += l;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+    first += __shfl_xor_sync(0xffffffffu, first, o);
+    total += __shfl_xor_sync(0xffffffffu, total, o);
+  }
+  if (lane == 0) {
+    seg_base[blockIdx.x] = inbox_bufs[owner] + (size_t)b * row_bytes;
+    if (owner == rank && local_offsets != nullptr) {
+      local_offsets[e] = first;
+      if (e == el - 1) local_offsets[el] = total;
+    }
+  }
+}
 }  // namespace
 }  // namespace moe
 
@@ -262,6 +296,22 @@ extern "C" int moe_ep_row_targets(void* const* home_bufs, const int32_t* counts_
       reinterpret_cast<char* const*>(home_bufs), counts_all, experts, world, rank, (size_t)d * elem_bytes,
       reinterpret_cast<char**>(row_ptrs));
   return check_launch("ep_row_targets_kernel");
+}
+
+extern "C" int moe_ep_segment_bases(void* const* inbox_bufs, const int32_t* counts_all, int experts, int world,
+                                    int rank, int d, int elem_bytes, void** seg_base, int32_t* local_offsets,
+                                    void* stream) {
+  using namespace moe;
+  if (experts <= 0 || world <= 0 || experts % world != 0)
+    return fail(MOE_ERR_ARG, "experts must be divisible by world_size");
+  if (rank < 0 || rank >= world) return fail(MOE_ERR_ARG, "moe_ep_segment_bases: bad rank");
+  if (d <= 0 || (elem_bytes != 2 && elem_bytes != 4) || ((size_t)d * elem_bytes) % 16 != 0)
+    return fail(MOE_ERR_ARG, "moe_ep_segment_bases: rows must be a multiple of 16 bytes");
+  if (!inbox_bufs || !counts_all || !seg_base) return fail(MOE_ERR_ARG, "moe_ep_segment_bases: null pointer");
+  ep_segment_bases_kernel<<<experts, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<char* const*>(inbox_bufs), counts_all, experts, world, rank, (size_t)d * elem_bytes,
+      reinterpret_cast<char**>(seg_base), local_offsets);
+  return check_launch("ep_segment_bases_kernel");
 }
 
 extern "C" int moe_enable_peer_access(int peer_device) {

@@ -166,13 +166,15 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
                          int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
                          char* __restrict__ packed, int32_t* __restrict__ row_route,
                          int32_t* __restrict__ route_row, int tokens, size_t row_bytes, int experts,
-                         int top_k, int num_tiles, int nbuf, int chunk_bytes, int32_t* status) {
+                         int top_k, int num_tiles, int nbuf, int chunk_bytes, int32_t* status,
+                         char* const* __restrict__ seg_base) {
   extern __shared__ __align__(128) uint8_t s_raw[];
   uint8_t* s_buf = s_raw;                                                        // [nbuf][chunk_bytes]
   uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_buf + (size_t)nbuf * chunk_bytes);  // [nbuf]
   int32_t* s_base = reinterpret_cast<int32_t*>(s_bar + nbuf);                    // [experts]
   int32_t* s_total = s_base + experts;                                           // [experts]
   int32_t* s_dst = s_total + experts;                                            // [kMaxTileRoutes]
+  int32_t* s_exp = s_dst + kMaxTileRoutes;                                       // [kMaxTileRoutes], seg_base only
 
   const int tile = blockIdx.x;
   const int lane = threadIdx.x & 31;
@@ -180,7 +182,7 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
   const int t0 = tile * kTileTokens;
   const int tile_tokens = min(kTileTokens, tokens - t0);
   const int chunks = (int)((row_bytes + chunk_bytes - 1) / chunk_bytes);
-  const int items = packed != nullptr ? tile_tokens * chunks : 0;
+  const int items = (packed != nullptr || seg_base != nullptr) ? tile_tokens * chunks : 0;
   const int depth = nbuf / kBulkIssuers;  // buffers owned by each issuing thread
 
   if (threadIdx.x == 0) {
@@ -214,7 +216,7 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
   asm volatile("griddepcontrol.wait;" ::: "memory");
   tile_destinations(idx, tile_hist, tile_base, counts, offsets, row_route, route_row, tile, t0,
                     tile_tokens * top_k, experts, top_k, num_tiles, blockIdx.x == 0, true, s_base, s_total,
-                    s_dst, status);
+                    s_dst, status, seg_base != nullptr ? s_exp : nullptr);
 
   if (lane == 0) {
     bool ok = true;
@@ -229,8 +231,16 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
       (void)item_src(it, bytes);
       for (int j = 0; j < top_k; ++j) {
         const int d = s_dst[row * top_k + j];
-        if (d >= 0)
-          bulk_store(packed + (size_t)d * row_bytes + (size_t)ch * chunk_bytes, buf0 + (uint32_t)b * chunk_bytes, bytes);
+        if (d < 0) continue;
+        char* dst_row;
+        if (seg_base == nullptr) {
+          dst_row = packed + (size_t)d * row_bytes;
+        } else {
+          // rows of expert e form one segment that starts at seg_base[e] (possibly in a peer's memory)
+          const int e = s_exp[row * top_k + j];
+          dst_row = seg_base[e] + (size_t)(d - s_total[e]) * row_bytes;
+        }
+        bulk_store(dst_row + (size_t)ch * chunk_bytes, buf0 + (uint32_t)b * chunk_bytes, bytes);
       }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       const int nxt = it + depth * kBulkIssuers;
@@ -275,7 +285,7 @@ int pick_split(int num_tiles) {
 int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d,
                         int experts, int top_k, int32_t* counts, int32_t* offsets, void* packed,
                         int32_t* row_route, int32_t* route_row, const Workspace& ws,
-                        cudaStream_t s) {
+                        cudaStream_t s, void* const* seg_base = nullptr) {
   if (tokens == 0) {
     pack_zero_kernel<<<(experts + 256) / 256, 256, 0, s>>>(counts, offsets, experts);
     return check_launch("pack_zero_kernel");
@@ -308,10 +318,11 @@ int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int t
   cfg.numAttrs = (tile_base == nullptr && pdl_enabled()) ? 1 : 0;
   cudaError_t err;
 
-  if ((align & 15) == 0 && packed != nullptr) {
+  char* const* sb = reinterpret_cast<char* const*>(seg_base);
+  if ((align & 15) == 0 && (packed != nullptr || sb != nullptr)) {
     const int chunk = (int)(row_bytes < (size_t)kChunkBytes ? row_bytes : (size_t)kChunkBytes);
     const int chunks = (int)((row_bytes + chunk - 1) / chunk);
-    const size_t fixed = (size_t)(2 * experts + kMaxTileRoutes) * sizeof(int32_t) + 64 * sizeof(uint64_t) + 128;
+    const size_t fixed = (size_t)(2 * experts + 2 * kMaxTileRoutes) * sizeof(int32_t) + 64 * sizeof(uint64_t) + 128;
     int nbuf = (int)((227 * 1024 - fixed) / chunk);
     const int want = ((kTileTokens * chunks + kBulkIssuers - 1) / kBulkIssuers) * kBulkIssuers;
     if (nbuf > want) nbuf = want;
@@ -319,17 +330,20 @@ int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int t
     nbuf = (nbuf / kBulkIssuers) * kBulkIssuers;
     if (nbuf >= kBulkIssuers) {
       const size_t smem = (size_t)nbuf * chunk + (size_t)nbuf * sizeof(uint64_t) +
-                         (size_t)(2 * experts + kMaxTileRoutes) * sizeof(int32_t);
+                         (size_t)(2 * experts + 2 * kMaxTileRoutes) * sizeof(int32_t);
       err = cudaFuncSetAttribute(pack_scatter_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_bulk_kernel: %s", cudaGetErrorString(err));
       cfg.gridDim = dim3(nt, 1, 1);
       cfg.dynamicSmemBytes = smem;
       err = cudaLaunchKernelEx(&cfg, pack_scatter_bulk_kernel, xs, idx, th, tile_base, counts, offsets, ps,
-                               row_route, route_row, tokens, row_bytes, experts, top_k, nt, nbuf, chunk, st);
+                               row_route, route_row, tokens, row_bytes, experts, top_k, nt, nbuf, chunk, st, sb);
       if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_bulk_kernel: %s", cudaGetErrorString(err));
       return MOE_OK;
     }
   }
+  if (sb != nullptr)
+    return fail(MOE_ERR_UNSUPPORTED, "moe_pack_scatter_to: rows must be a multiple of 16 bytes, 16-byte aligned, "
+                                     "and fit the staging ring");
 
   const int split = pick_split(nt);
   cfg.gridDim = dim3(nt * split, 1, 1);
@@ -506,5 +520,28 @@ extern "C" int moe_pack_scatter(const void* x, int elem_bytes, const int32_t* id
                 workspace_bytes_for(tokens, experts, top_k));
   Workspace ws = carve(workspace, tokens, experts);
   return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, packed, row_route,
-                             route_row, ws, static_cast<cudaStream_t>(stream));
+                             route_row, ws, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+// The scatter with one destination segment per expert: the rows routed to expert e are stored, in
+// canonical order, from seg_base[e] on (device array of `experts` 16-byte aligned addresses), instead
+// of at packed[offsets[e]].  The expert-parallel layer points every segment into the inbox of the rank
+// that owns the expert (a peer mapping, bulk stores over NVLink): dispatch without a local packed copy.
+extern "C" int moe_pack_scatter_to(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
+                                   int top_k, int32_t* counts, int32_t* offsets, void* const* seg_base,
+                                   int32_t* row_route, int32_t* route_row, void* workspace, size_t workspace_bytes,
+                                   void* stream) {
+  using namespace moe;
+  if (tokens < 0 || d <= 0 || experts <= 0) return fail(MOE_ERR_ARG, "moe_pack_scatter_to: bad shape");
+  if (top_k < 1 || top_k > 8) return fail(MOE_ERR_UNSUPPORTED, "moe_pack_scatter_to: top_k must be in [1,8], got %d", top_k);
+  if (experts > 1024) return fail(MOE_ERR_UNSUPPORTED, "moe_pack_scatter_to: experts must be <= 1024");
+  if (elem_bytes != 2 && elem_bytes != 4) return fail(MOE_ERR_ARG, "moe_pack_scatter_to: elem_bytes must be 2 or 4");
+  if (!counts || !offsets || !seg_base) return fail(MOE_ERR_ARG, "moe_pack_scatter_to: null counts/offsets/seg_base");
+  if (tokens > 0 && (!idx || !row_route || !x)) return fail(MOE_ERR_ARG, "moe_pack_scatter_to: null pointer");
+  if (!workspace || workspace_bytes < workspace_bytes_for(tokens, experts, top_k))
+    return fail(MOE_ERR_WORKSPACE, "moe_pack_scatter_to: workspace too small (need %zu bytes)",
+                workspace_bytes_for(tokens, experts, top_k));
+  Workspace ws = carve(workspace, tokens, experts);
+  return launch_scan_scatter(x, elem_bytes, idx, tokens, d, experts, top_k, counts, offsets, nullptr, row_route,
+                             route_row, ws, static_cast<cudaStream_t>(stream), seg_base);
 }

@@ -15,8 +15,9 @@ constexpr int kChunkBytes = 8192;                // a row longer than this moves
 // routes to e in earlier tiles.  With tile_base == nullptr every CTA derives both from the tile
 // histograms itself (they are L2-resident and small); otherwise pack_scan_kernel has produced
 // tile_base and counts.  Then warp 0 ranks the routes of the tile with match/ballot.  On return
-// s_dst[r] holds the destination row of route r of the tile (-1 = skip) and the maps are written.
-// `publish` marks the one CTA of the grid that writes counts and offsets.
+// s_dst[r] holds the destination row of route r of the tile (-1 = skip) and the maps are written;
+// s_total[e] holds offsets[e] (first row of expert e) and, when s_exp is given, s_exp[r] the expert
+// of route r.  `publish` marks the one CTA of the grid that writes counts and offsets.
 __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ idx,
                                                   const int32_t* __restrict__ tile_hist,
                                                   const int32_t* __restrict__ tile_base,
@@ -25,7 +26,8 @@ __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ id
                                                   int32_t* __restrict__ route_row, int tile, int t0,
                                                   int tile_routes, int experts, int top_k, int num_tiles,
                                                   bool publish, bool write_maps, int32_t* s_base,
-                                                  int32_t* s_total, int32_t* s_dst, int32_t* status) {
+                                                  int32_t* s_total, int32_t* s_dst, int32_t* status,
+                                                  int32_t* s_exp = nullptr) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   // warp 0 ranks the routes later; it fetches their expert ids now so that the loads overlap the
@@ -109,6 +111,7 @@ __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ id
       if (e < experts) {
         const int excl = carry + incl - c;
         s_base[e] += excl;
+        s_total[e] = excl;
         if (publish) {
           offsets[e] = excl;
           if (tile_base == nullptr) counts[e] = c;
@@ -141,6 +144,7 @@ __device__ __forceinline__ void tile_destinations(const int32_t* __restrict__ id
       if (in_tile) {
         const int dst = valid ? base + rank : -1;
         s_dst[r] = dst;
+        if (s_exp != nullptr) s_exp[r] = e;
         if (valid && write_maps) {
           const int route = t0 * top_k + r;
           row_route[dst] = route;

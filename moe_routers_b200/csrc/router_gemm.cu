@@ -587,7 +587,7 @@ int check_router_args(const char* who, const void* x, const void* w, int tokens,
 
 int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int tokens, int d, int experts,
                         int top_k, int32_t* counts, int32_t* offsets, void* packed, int32_t* row_route,
-                        int32_t* route_row, const Workspace& ws, cudaStream_t s);
+                        int32_t* route_row, const Workspace& ws, cudaStream_t s, void* const* seg_base = nullptr);
 
 }  // namespace moe
 

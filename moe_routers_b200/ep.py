@@ -111,6 +111,9 @@ class EPMoELayer:
         # peer transport: the second expert GEMM stores its result rows straight into the home ranks'
         # packed slots (one kernel computes and returns); False: dense result + a separate push
         self.fuse_combine = True
+        # peer transport: the pack stores every row straight into the owner's inbox (no local packed
+        # copy, no push kernel); False: pack locally, then push
+        self.direct_dispatch = True
         self._peer = None
         self.comm_stream = torch.cuda.Stream()
         # Expert groups pipelined against the exchanges, and SMs the persistent GEMM leaves to the
@@ -133,6 +136,30 @@ class EPMoELayer:
             return dict(idx=idx, gates=gates, counts=counts, offsets=offsets, packed=packed,
                         row_route=row_route, route_row=route_row)
         return ops.route_fused(x, self.w_router, self.k, skew_experts=self.skew_experts, skew_bias=self.skew_bias)
+
+    def route_select(self, x):
+        """Select + pack plan without copying a row: idx, gates, counts, offsets, the route <-> row maps
+        and the scratch buffer holding the tile histograms (input of the direct dispatch)."""
+        if self.strategy == "sinkhorn":
+            _, _, logits = ops.router_gemm_select(x, self.w_router, self.k, skew_experts=self.skew_experts,
+                                                  skew_bias=self.skew_bias, return_logits=True)
+            idx, gates = ops.sinkhorn(logits, self.k, iters=self.sinkhorn_iters,
+                                      temperature=self.sinkhorn_temperature)
+            o = ops.route_plan(x, idx, self.e)
+        else:
+            idx, gates = ops.router_gemm_select(x, self.w_router, self.k, skew_experts=self.skew_experts,
+                                                skew_bias=self.skew_bias)
+            o = ops.route_plan(x, idx, self.e, hist_ready=True)
+        o["gates"] = gates
+        return o
+
+    def dispatch_direct(self, x, o, counts_all):
+        """Store every routed row of x straight into its owner's expert-major inbox."""
+        pr = self._peer
+        check(lib.moe_ep_segment_bases(pr["inbox_ptrs"].data_ptr(), counts_all.data_ptr(), self.e, self.world,
+                                       self.rank, pr["d"], x.element_size(), pr["seg_base"].data_ptr(),
+                                       pr["offsets"].data_ptr(), torch.cuda.current_stream().cuda_stream))
+        ops.pack_scatter_to(x, self.e, o, pr["seg_base"])
 
     def exchange_counts(self, counts):
         """All-gather the per-expert counts; returns (device [W,E] int32, host copy).  One host sync,
@@ -271,6 +298,7 @@ class EPMoELayer:
             home_ptrs=torch.tensor(home_ptrs, dtype=torch.int64, device=device),
             yb=torch.empty((cap, d), dtype=dtype, device=device),
             targets=torch.zeros(cap, dtype=torch.int64, device=device),
+            seg_base=torch.zeros(self.e, dtype=torch.int64, device=device),
             offsets=torch.zeros(self.el + 1, dtype=torch.int32, device=device),
             flag=torch.zeros(1, dtype=torch.int32, device=device),
         )
@@ -302,17 +330,21 @@ class EPMoELayer:
         dist.all_reduce(self._peer["flag"], group=self.group)
 
     def forward_peer(self, x: torch.Tensor) -> torch.Tensor:
-        o = self.route(x)
-        packed = o["packed"]
-        rows_home, d = packed.shape
+        x = x.contiguous()
+        rows_home, d = x.size(0) * self.k, x.size(1)
+        direct = self.direct_dispatch and (d * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
+        o = self.route_select(x) if direct else self.route(x)
         if self._peer is None or self._peer["rows_home"] != rows_home or self._peer["d"] != d:
-            self._setup_peer(rows_home, d, packed.dtype, packed.device)
+            self._setup_peer(rows_home, d, x.dtype, x.device)
         pr = self._peer
         counts_all = torch.empty((self.world, self.e), dtype=torch.int32, device=x.device)
         dist.all_gather_into_tensor(counts_all, o["counts"], group=self.group)
         # every rank has left the previous call's combine before anybody overwrites an inbox: the
         # all-gather above is that barrier (it completes only when every rank has reached it)
-        self._push(packed, pr["inbox_ptrs"], counts_all, False, pr["offsets"])
+        if direct:
+            self.dispatch_direct(x, o, counts_all)
+        else:
+            self._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
         if self.fuse_combine:
             targets = self._row_targets(counts_all)
             self._rank_sync()  # all rows have arrived in every inbox

@@ -116,6 +116,50 @@ def pack_scatter(x: torch.Tensor, experts: int, out: dict) -> dict:
     return out
 
 
+def route_plan(x: torch.Tensor, idx: torch.Tensor, experts: int, *, hist_ready: bool = False) -> dict:
+    """Counts, offsets and the route <-> row maps of a pack, without copying a row.
+
+    `hist_ready`: the per-tile histograms of `idx` are already in the calling stream's scratch buffer
+    (router_gemm_select has just produced idx on this stream); otherwise they are computed from idx.
+    Returns dict(idx, counts, offsets, row_route, route_row, workspace) for `pack_scatter_to`."""
+    _require_cuda(x, idx)
+    idx = idx.to(torch.int32).contiguous()
+    t, d = x.shape
+    k = idx.size(1)
+    dev = x.device
+    with torch.cuda.device(dev):
+        o = dict(idx=idx, counts=torch.empty(experts, dtype=torch.int32, device=dev),
+                 offsets=torch.empty(experts + 1, dtype=torch.int32, device=dev),
+                 row_route=torch.empty(t * k, dtype=torch.int32, device=dev),
+                 route_row=torch.empty(t * k, dtype=torch.int32, device=dev))
+        ws = o["workspace"] = workspace(dev, t, experts, k)
+        fn = lib.moe_pack_scatter if hist_ready else lib.moe_pack
+        check(fn(x.data_ptr(), x.element_size(), idx.data_ptr(), t, d, int(experts), k, o["counts"].data_ptr(),
+                 o["offsets"].data_ptr(), None, o["row_route"].data_ptr(), o["route_row"].data_ptr(),
+                 ws.data_ptr(), ws.numel(), _stream()))
+    return o
+
+
+def pack_scatter_to(x: torch.Tensor, experts: int, plan: dict, seg_base: torch.Tensor) -> dict:
+    """Scatter the token rows of a planned route to one destination segment per expert: rows of expert
+    e go, in canonical order, to the address seg_base[e] onwards (int64 [experts] on the device;
+    16-byte aligned; peers' mapped memory allowed).  `plan` comes from `route_plan` (or route_fused)
+    for the same x; its histograms must still be in plan["workspace"]."""
+    _require_cuda(x, seg_base)
+    if seg_base.dtype != torch.int64 or seg_base.numel() < experts:
+        raise RuntimeError("seg_base must be an int64 tensor with one address per expert")
+    x = x.contiguous()
+    t, d = x.shape
+    k = plan["idx"].size(1)
+    ws = plan["workspace"]
+    with torch.cuda.device(x.device):
+        check(lib.moe_pack_scatter_to(x.data_ptr(), x.element_size(), plan["idx"].data_ptr(), t, d, int(experts), k,
+                                      plan["counts"].data_ptr(), plan["offsets"].data_ptr(), seg_base.data_ptr(),
+                                      plan["row_route"].data_ptr(), plan["route_row"].data_ptr(), ws.data_ptr(),
+                                      ws.numel(), _stream()))
+    return plan
+
+
 def fused_select(logits: torch.Tensor, x: torch.Tensor, experts: int, top_k: int, out: Optional[tuple] = None):
     """Select + count + scan + pack from given logits in two launches.
     Returns (idx, gates, counts, offsets, packed, row_route, route_row); `out` may be the tuple a

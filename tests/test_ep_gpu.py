@@ -149,6 +149,54 @@ def test_row_targets_and_gemm_return_emulated_ranks(world, e, d):
         assert home_a[r][:n_home[r]].abs().sum() > 0 or n_home[r] == 0
 
 
+@pytest.mark.parametrize("world,e,d,k", [(4, 16, 64, 2), (2, 8, 128, 1), (8, 64, 4096, 2), (1, 4, 64, 3)])
+def test_direct_dispatch_emulated_ranks(world, e, d, k):
+    """Dispatch fused into the pack, all ranks emulated on one GPU: moe_pack_scatter_to with the
+    segment bases of moe_ep_segment_bases must fill every owner's inbox exactly as pack + dispatch
+    push does (itself checked against numpy above), and the plan must equal the pack's outputs."""
+    _need_cuda()
+    from moe_routers_b200 import _lib, ops
+
+    el = e // world
+    rng = np.random.default_rng(7 * world + e + k)
+    tokens = [int(rng.integers(40, 300)) for _ in range(world)]
+    xs = [torch.from_numpy(rng.standard_normal((t, d)).astype(np.float16)).cuda() for t in tokens]
+    idxs = []
+    for t in tokens:
+        scores = rng.random((t, e))
+        scores[:, 0] += 0.5  # a hot expert
+        idxs.append(torch.from_numpy(np.argsort(-scores, axis=1)[:, :k].astype(np.int32)).cuda())
+    counts_all = np.stack([np.bincount(i.cpu().numpy().reshape(-1), minlength=e) for i in idxs]).astype(np.int32)
+    c_t = torch.from_numpy(counts_all).cuda()
+    cap = int(counts_all.sum()) + 1
+    inbox_a = [torch.zeros((cap, d), dtype=torch.float16, device="cuda") for _ in range(world)]
+    inbox_b = [torch.zeros_like(t) for t in inbox_a]
+    ptr_a = torch.tensor([t.data_ptr() for t in inbox_a], dtype=torch.int64, device="cuda")
+    ptr_b = torch.tensor([t.data_ptr() for t in inbox_b], dtype=torch.int64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for r in range(world):
+        counts, offsets, packed, row_route, route_row = ops.pack(xs[r], idxs[r], e)
+        off_a = torch.full((el + 1,), -1, dtype=torch.int32, device="cuda")
+        _lib.check(_lib.lib.moe_ep_push(packed.data_ptr(), ptr_a.data_ptr(), c_t.data_ptr(), e, world, r, 0, d, 2,
+                                        off_a.data_ptr(), st))
+        plan = ops.route_plan(xs[r], idxs[r], e)
+        for key, ref in (("counts", counts), ("offsets", offsets), ("row_route", row_route), ("route_row", route_row)):
+            assert torch.equal(plan[key], ref), key
+        seg = torch.zeros(e, dtype=torch.int64, device="cuda")
+        off_b = torch.full((el + 1,), -1, dtype=torch.int32, device="cuda")
+        _lib.check(_lib.lib.moe_ep_segment_bases(ptr_b.data_ptr(), c_t.data_ptr(), e, world, r, d, 2, seg.data_ptr(),
+                                                 off_b.data_ptr(), st))
+        ops.pack_scatter_to(xs[r], e, plan, seg)
+        assert torch.equal(off_a, off_b)
+        for key, ref in (("counts", counts), ("offsets", offsets), ("row_route", row_route), ("route_row", route_row)):
+            assert torch.equal(plan[key], ref), key
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    for p_ in range(world):
+        assert torch.equal(inbox_a[p_], inbox_b[p_])
+        assert inbox_a[p_].abs().sum() > 0
+
+
 def _ep_worker(rank, world, port, strategy, q):
     try:
         import torch.distributed as dist
@@ -176,6 +224,7 @@ def _ep_worker(rank, world, port, strategy, q):
             layer = layers[tr]
             if fuse is not None:
                 layer.fuse_combine = fuse  # second GEMM returns its rows itself / dense result + push
+                layer.direct_dispatch = fuse  # pack stores into the owners' inboxes / local pack + push
             out = layer(x.cuda(), overlap=overlap)
             torch.cuda.synchronize()
             outs[(tr, fuse)] = out.clone()
