@@ -339,7 +339,7 @@ def main_ours(args):
                                sinkhorn_temperature=1.0, warmup=2, iters=5, skew_experts=sn, skew_bias=sb, transport="peer")
             r = bench_ep.run(ns)[0]
             ep[tag] = {k: r[k] for k in ("t_route_us", "t_comm_us", "t_comp_us", "t_combine_us", "t_layer_seq_us",
-                                         "t_layer_overlap_us", "eta_overlap", "load_max_over_mean", "load_cv",
+                                         "t_layer_overlap_us", "t_layer_back_to_back_us", "eta_overlap", "load_max_over_mean", "load_cv",
                                          "tokens_per_s")}
     except Exception as exc:  # the route numbers above stand on their own
         ep = {"error": f"{type(exc).__name__}: {exc}"}

@@ -203,7 +203,10 @@ def _ep_worker(rank, world, port, strategy, q):
 
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         torch.cuda.set_device(rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import datetime
+
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=90))
         from moe_routers_b200.ep import EPMoELayer
 
         t, d, h, e, k = 512 + 64 * rank, 256, 512, 16, 2
@@ -258,11 +261,26 @@ def _run_ranks(world, strategy):
     procs = [ctx.Process(target=_ep_worker, args=(r, world, port, strategy, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in procs]
+    # A rank that raises leaves its peers waiting in a collective: stop them as soon as the first
+    # failure is known (or nothing has been heard for two minutes) instead of waiting them out.
+    import queue
+
+    results = []
+    try:
+        while len(results) < world:
+            results.append(q.get(timeout=120))
+            if results[-1][1] != "ok":
+                break
+    except queue.Empty:
+        results.append((-1, "no result from the remaining ranks within 120 s"))
     for p in procs:
-        p.join(timeout=60)
+        p.join(timeout=20 if all(m == "ok" for _, m in results) else 1)
+        if p.is_alive():
+            p.terminate()
+            p.join(timeout=10)
     for rank, msg in results:
         assert msg == "ok", f"rank {rank}: {msg}"
+    assert len(results) == world
 
 
 @pytest.mark.parametrize("strategy", ["fused_select", "sinkhorn"])
