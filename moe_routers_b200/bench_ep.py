@@ -180,7 +180,7 @@ def main() -> None:
         results = run(args)
         if dist.get_rank() == 0:
             print("=== EP MoE layer (us, mean over iters, max over ranks) ===")
-            print(f"{'strategy':<13}{'T_route':>9}{'T_comm':>9}{'T_comp':>10}{'T_comb':>8}{'T(seq)':>10}{'T(ovl)':>10}"
+            print(f"{'strategy':<13}{'T_route':>9}{'T_comm':>9}{'T_comp':>10}{'T_comb':>8}{'T(seq)':>10}{'T(ovl)':>10}{'T(b2b)':>10}"
                   f"{'eta':>6}{'max/mean':>9}{'CV':>6}")
             for r in results:
                 print(f"{r['strategy']:<13}{r['t_route_us']:9.1f}{r['t_comm_us']:9.1f}{r['t_comp_us']:10.1f}"
