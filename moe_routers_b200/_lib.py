@@ -11,6 +11,7 @@ import os
 from .build import LIB_PATH
 
 MOE_OK = 0
+MOE_ERR_ARG, MOE_ERR_UNSUPPORTED, MOE_ERR_WORKSPACE, MOE_ERR_LAUNCH, MOE_ERR_DEVICE = 1, 2, 3, 4, 5  # include/moe_b200.h
 MOE_F16, MOE_BF16, MOE_F32 = 0, 1, 2
 MOE_ACT_NONE, MOE_ACT_GELU, MOE_ACT_SILU, MOE_ACT_SWIGLU = 0, 1, 2, 3
 MOE_W_KN, MOE_W_NK = 0, 1
