@@ -133,6 +133,14 @@ def run_cpu_reference(steps: int, warmup: int):
     import torch
     from oracle import cpu_route
 
+    # all host threads this process may use (a multi-rank launcher exports OMP_NUM_THREADS=1, which
+    # would make the baseline single-threaded; only one rank runs it, so it takes the whole host)
+    try:
+        n_cpu = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n_cpu = os.cpu_count() or 1
+    if torch.get_num_threads() < n_cpu:
+        torch.set_num_threads(n_cpu)
     x, w = gen_inputs_cpu(0)
     for _ in range(max(1, warmup)):
         cpu_route.one_iter(x, w, K_TOP, skew_experts=SKEW_N, skew_bias=SKEW_B)
