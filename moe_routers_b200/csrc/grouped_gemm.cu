@@ -11,7 +11,8 @@
 // per-call pointer table.  Tiles of one expert that share a weight n-tile are adjacent in the
 // list, so CTAs that run at the same time read the same weight tile through L2.
 //
-// Tile 128 x BN x 64, UMMA 128 x BN x 16 (fp16 in, fp32 accumulate in TMEM).  Two TMEM accumulators:
+// Tile 128 x BN x 64, UMMA 128 x BN x 16 (fp16 in, fp32 accumulate in TMEM); an expert's last tile
+// with at most 64 rows is issued as UMMA 64 x BN x 16 instead.  Two TMEM accumulators:
 // the epilogue of tile i (TMEM -> registers -> activation -> fp16 -> global, rows past the end of
 // the expert's segment masked) overlaps the main loop of tile i+1.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
@@ -24,6 +25,8 @@
 // (plain 128-bit stores; no TMA and no multicast on peer memory).  The epilogue warp stages 32 rows
 // x 64 columns in shared memory and stores them as 128-byte row pieces, 4 rows per instruction,
 // so that a peer store is a full 128-byte write, not 32 scattered 16-byte ones.
+#include <cstdlib>
+
 #include "sm100.cuh"
 
 namespace moe {
@@ -49,6 +52,7 @@ struct GParams {
   int bf16;              // 0: fp16 data, 1: bf16 data
   uint16_t* c;
   uint16_t* const* c_rows;  // null: dense C; else base address of every output row
+  int m64;                  // 1: a last tile of <= 64 rows runs as UMMA M=64; 0: every tile is 128 rows
   int32_t* status;
 };
 
@@ -261,12 +265,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(kBM, BN, p.bf16, 0, p.w_kn);
+      const uint32_t idesc128 = make_idesc_f16(kBM, BN, p.bf16, 0, p.w_kn);
+      const uint32_t idesc64 = make_idesc_f16(64, BN, p.bf16, 0, p.w_kn);
       uint32_t it = 0;
       int local = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const int ab = local & 1;
+        uint32_t idesc = idesc128;
+        if (p.m64) {
+          // a last tile that holds at most 64 rows of its expert costs half the tensor time as M=64
+          int e, nt, mt;
+          decode_tile(s_mt, p.experts, p.n_tiles, t, e, nt, mt);
+          if (min(p.offsets[e + 1], p.rows) - (p.offsets[e] + mt * kBM) <= 64) idesc = idesc64;
+        }
         if (!mbar_wait(tempty0 + 8 * ab, (((uint32_t)local >> 1) & 1u) ^ 1u, p.status, 4)) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
@@ -301,8 +313,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       decode_tile(s_mt, p.experts, p.n_tiles, t, e, nt, mt);
       const int ab = local & 1;
       const int seg_end = min(p.offsets[e + 1], p.rows);
-      const int grow = p.offsets[e] + mt * kBM + q * 32 + lane;
-      const bool valid = grow < seg_end && grow >= 0;
+      const int row0 = p.offsets[e] + mt * kBM;
+      int trow = q * 32 + lane;  // row of the tile held by this thread's TMEM lane
+      bool lane_used = true;
+      if (p.m64 && seg_end - row0 <= 64) {
+        // the M=64 accumulator keeps 16 rows in each 32-lane TMEM quarter (lanes 0..15 of the quarter)
+        trow = q * 16 + lane;
+        lane_used = lane < 16;
+      }
+      const int grow = row0 + trow;
+      const bool valid = lane_used && grow < seg_end && grow >= 0;
       if (!mbar_wait(tfull0 + 8 * ab, ((uint32_t)local >> 1) & 1u, p.status, 3)) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
@@ -385,6 +405,12 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
   p.row_scale = row_scale;
   p.c = static_cast<uint16_t*>(c);
   p.c_rows = reinterpret_cast<uint16_t* const*>(c_rows);
+  {
+    // MOE_B200_M64=0 in the environment keeps every tile at 128 rows (the default runs an expert's
+    // last tile as UMMA M=64 when it holds at most 64 rows: half the tensor time for that tile)
+    static const int m64 = [] { const char* v = getenv("MOE_B200_M64"); return (v && v[0] == '0') ? 0 : 1; }();
+    p.m64 = m64;
+  }
   p.bias = static_cast<const uint16_t*>(bias);
   p.bf16 = dtype == MOE_BF16;
   p.status = static_cast<int32_t*>(workspace);
