@@ -65,6 +65,13 @@ CASES = [
     ([24, 24, 7], 32, 64, "nk", "swiglu"),
     ([50, 3], 72, 48, "nk", "gelu"),
     ([50, 3], 64, 16, "nk", "swiglu"),
+    # average >= 512 rows per expert and 256 accumulator columns: work units are pairs of 128-row
+    # tiles sharing the weight stages (odd tile counts, empty experts, short last tiles included)
+    ([600, 256, 300, 1000], 192, 256, "nk", None),
+    ([600, 0, 150, 1300], 256, 512, "nk", "gelu"),
+    ([385, 640, 1, 1030], 320, 256, "kn", None),
+    ([600, 256, 300, 1000], 128, 128, "nk", "swiglu"),
+    ([257, 513, 769, 564], 192, 256, "kn", "swiglu"),
 ]
 
 
@@ -180,11 +187,12 @@ def test_demo_pipeline_on_device(ops):
 @pytest.mark.parametrize("N,act,dtype,bias", [(512, None, torch.float16, False), (256, "gelu", torch.float16, True),
                                               (128, "swiglu", torch.bfloat16, False), (64, None, torch.float16, False),
                                               (48, "silu", torch.float16, True), (1024, "swiglu", torch.float16, True)])
-def test_grouped_gemm_scattered_rows_equal_dense(ops, N, act, dtype, bias):
+@pytest.mark.parametrize("counts", [[130, 0, 257, 1, 64, 300], [600, 0, 257, 1230]])
+def test_grouped_gemm_scattered_rows_equal_dense(ops, N, act, dtype, bias, counts):
     """`out_rows`: every result row stored at its own address.  With the addresses of a permuted
     buffer the result must be the dense result, row-permuted, bit for bit (same kernel arithmetic);
-    rows that no address points to stay untouched."""
-    counts = [130, 0, 257, 1, 64, 300]
+    rows that no address points to stay untouched.  (The second set of counts runs in pair mode
+    where the tile has 256 accumulator columns.)"""
     K = 192
     off = _segments(counts)
     rows, e = int(off[-1]), len(counts)
