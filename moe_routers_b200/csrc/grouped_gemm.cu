@@ -185,6 +185,28 @@ __device__ __forceinline__ void store_staged_rows(const uint8_t* stage, uint16_t
   }
 }
 
+// The weight boxes of one stage: f(byte offset inside the stage's B area, tensor-map coordinates).
+template <typename F>
+__device__ __forceinline__ void for_each_weight_box(const GParams& p, int BN, bool swiglu, int kb, int nt, int e, F&& f) {
+  const int half = BN / 2;
+  if (!p.w_kn) {
+    // weights [E, Nw, K]: K-major B, one box of BN rows (SwiGLU: gate rows and up rows)
+    if (!swiglu) {
+      f(0u, kb * kBK, nt * BN, e);
+    } else {
+      f(0u, kb * kBK, nt * half, e);
+      f((uint32_t)half * kBK * 2, kb * kBK, p.n_out + nt * half, e);
+    }
+  } else {
+    // weights [E, K, Nw]: MN-major B, boxes of 64 (N) x 64 (K), one per 64 output columns
+    for (int j = 0; j < BN / 64; ++j) {
+      int ncol = nt * BN + j * 64;
+      if (swiglu) ncol = (j < BN / 128) ? nt * half + j * 64 : p.n_out + nt * half + (j - BN / 128) * 64;
+      f((uint32_t)j * 8192u, ncol, kb * kBK, e);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const GParams p) {
@@ -281,7 +303,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.n_tiles, pair, t);
         const int e = u.e, nt = u.nt, row0 = u.row0;
         const bool two = u.two;  // the unit has a second tile
-        const int half = BN / 2;
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = (int)(it % (uint32_t)n_stages);
           const uint32_t ph = (it / (uint32_t)n_stages) & 1u;
@@ -290,22 +311,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tma_load_2d(smem_u32(sA + (size_t)s * a_stage), &tmap_a, full0 + 8 * s, kb * kBK, row0);
           if (two) tma_load_2d(smem_u32(sA + (size_t)s * a_stage + kABytes), &tmap_a, full0 + 8 * s, kb * kBK, row0 + kBM);
           const uint32_t sb = smem_u32(sB + (size_t)s * b_bytes);
-          if (!p.w_kn) {
-            // weights [E, Nw, K]: K-major B, one box of BN rows (SwiGLU: gate rows and up rows)
-            if (!swiglu) {
-              tma_load_3d(sb, &tmap_w, full0 + 8 * s, kb * kBK, nt * BN, e);
-            } else {
-              tma_load_3d(sb, &tmap_w, full0 + 8 * s, kb * kBK, nt * half, e);
-              tma_load_3d(sb + (uint32_t)half * kBK * 2, &tmap_w, full0 + 8 * s, kb * kBK, p.n_out + nt * half, e);
-            }
-          } else {
-            // weights [E, K, Nw]: MN-major B, boxes of 64 (N) x 64 (K), one per 64 output columns
-            for (int j = 0; j < BN / 64; ++j) {
-              int ncol = nt * BN + j * 64;
-              if (swiglu) ncol = (j < BN / 128) ? nt * half + j * 64 : p.n_out + nt * half + (j - BN / 128) * 64;
-              tma_load_3d(sb + (uint32_t)j * 8192u, &tmap_w, full0 + 8 * s, ncol, kb * kBK, e);
-            }
-          }
+          for_each_weight_box(p, BN, swiglu, kb, nt, e, [&](uint32_t ofs, int c0, int c1, int c2) {
+            tma_load_3d(sb + ofs, &tmap_w, full0 + 8 * s, c0, c1, c2);
+          });
         }
       }
     }
