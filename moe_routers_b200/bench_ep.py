@@ -120,8 +120,11 @@ def run(args) -> list[dict]:
         # the layer called back to back (one event pair around all calls, no host synchronisation in
         # between): the host's launch work hides behind the previous call's expert GEMMs, as it does
         # inside a multi-layer model
-        dist.barrier()
-        acc["b2b"] = _event_us(lambda: [layer(x, overlap=True) for _ in range(args.iters)])
+        batches = []
+        for _ in range(3):  # median of three batches: one disturbed batch does not decide the figure
+            dist.barrier()
+            batches.append(_event_us(lambda: [layer(x, overlap=True) for _ in range(args.iters)]))
+        acc["b2b"] = sorted(batches)[1]
         vals = torch.tensor([acc[n] / args.iters for n in ("route", "comm", "comp", "combine", "seq", "ovl", "b2b")],
                             device=dev, dtype=torch.float64)
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
