@@ -14,6 +14,8 @@
 // follows, and every CTA adds the partials in the same fixed order (bit-identical b everywhere,
 // run-to-run deterministic).  One grid barrier per iteration; the grid is launched cooperatively so
 // that all CTAs are co-resident, and the barrier spin is bounded in time.
+#include <cstdlib>
+
 #include "sm100.cuh"
 
 namespace moe {
@@ -35,7 +37,7 @@ struct SParams {
 
 // CLUSTER = false: any number of co-resident CTAs (cooperative launch), column partials through a
 // global scratch and a grid barrier.  CLUSTER = true: the whole matrix fits the shared memory of
-// ONE thread-block cluster (8 CTAs x 1024 threads); column partials are pushed into every CTA's
+// ONE thread-block cluster (16 or 8 CTAs x 1024 threads); column partials are pushed into every CTA's
 // shared memory (st.shared::cluster) and a hardware cluster barrier replaces the grid barrier, which
 // takes the global-memory round trips out of every iteration.
 // One thread per row: scan q_ij = a_i K_ij b_j over the columns keeping the best KMAX entries under
@@ -241,7 +243,8 @@ sinkhorn_kernel(const SParams p) {
   SK_TRACE(61);
 }
 
-constexpr int kClusterCtas = 8;
+constexpr int kClusterCtas = 8;        // portable cluster size
+constexpr int kClusterCtasWide = 16;   // needs cudaFuncAttributeNonPortableClusterSizeAllowed
 constexpr int kClusterThreads = 1024;
 
 // Shared memory (bytes) of a launch with `rows` rows per CTA.
@@ -253,22 +256,40 @@ size_t sinkhorn_smem(int rows, int experts, int threads, int nblk, bool cluster)
   return floats * sizeof(float);
 }
 
+// Launch as ONE cluster of `ctas` CTAs.  Returns MOE_ERR_UNSUPPORTED (nothing launched, no error text
+// kept) when `probe` is set and the device cannot place such a cluster, so that the caller can fall
+// back to the portable size.
 template <typename T>
-int launch_sinkhorn_cluster(SParams& p, size_t smem, cudaStream_t s) {
+int launch_sinkhorn_cluster(SParams& p, int ctas, size_t smem, cudaStream_t s, bool probe) {
   cudaError_t e = cudaFuncSetAttribute(sinkhorn_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_sinkhorn: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  if (ctas > kClusterCtas) {
+    e = cudaFuncSetAttribute(sinkhorn_kernel<T, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return MOE_ERR_UNSUPPORTED;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(kClusterCtas, 1, 1);
+  cfg.gridDim = dim3(ctas, 1, 1);
   cfg.blockDim = dim3(kClusterThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = kClusterCtas;
+  attr[0].val.clusterDim.x = ctas;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (probe) {
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, sinkhorn_kernel<T, true>, &cfg);
+    if (e != cudaSuccess || clusters < 1) {
+      (void)cudaGetLastError();
+      return MOE_ERR_UNSUPPORTED;
+    }
+  }
   e = cudaLaunchKernelEx(&cfg, sinkhorn_kernel<T, true>, p);
   if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "sinkhorn_kernel (cluster): %s", cudaGetErrorString(e));
   return MOE_OK;
@@ -319,19 +340,26 @@ extern "C" int moe_sinkhorn(const void* logits, int logits_dtype, int tokens, in
   p.idx = idx; p.gates = gates; p.scratch = ws.fscratch; p.control = ws.control; p.status = ws.status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  // One cluster of 8 CTAs when the matrix fits its shared memory (T=4096, E=64 does): no global
-  // round trips inside the iterations.
-  {
-    const int rows = (tokens + kClusterCtas - 1) / kClusterCtas;
-    const size_t smem = sinkhorn_smem(rows, experts, kClusterThreads, kClusterCtas, true);
+  // One cluster when the matrix fits its shared memory (T=4096, E=64 does): no global round trips
+  // inside the iterations.  16 CTAs where the device can place such a cluster (half the rows per CTA:
+  // every pass of the iteration is shorter), else the portable 8.  MOE_B200_SINKHORN_CLUSTER=8 in the
+  // environment keeps the portable size.
+  static const int wide_ok = [] { const char* v = getenv("MOE_B200_SINKHORN_CLUSTER"); return !(v && atoi(v) == 8); }();
+  for (int ctas : {kClusterCtasWide, kClusterCtas}) {
+    if (ctas == kClusterCtasWide && (!wide_ok || tokens < 1024)) continue;
+    const int rows = (tokens + ctas - 1) / ctas;
+    const size_t smem = sinkhorn_smem(rows, experts, kClusterThreads, ctas, true);
     if (smem <= 200 * 1024 && tokens >= 256) {
       p.rows_per_cta = rows;
+      const bool probe = ctas == kClusterCtasWide;
+      int rc;
       switch (logits_dtype) {
-        case MOE_F16: return launch_sinkhorn_cluster<__half>(p, smem, s);
-        case MOE_BF16: return launch_sinkhorn_cluster<__nv_bfloat16>(p, smem, s);
-        case MOE_F32: return launch_sinkhorn_cluster<float>(p, smem, s);
+        case MOE_F16: rc = launch_sinkhorn_cluster<__half>(p, ctas, smem, s, probe); break;
+        case MOE_BF16: rc = launch_sinkhorn_cluster<__nv_bfloat16>(p, ctas, smem, s, probe); break;
+        case MOE_F32: rc = launch_sinkhorn_cluster<float>(p, ctas, smem, s, probe); break;
         default: return fail(MOE_ERR_ARG, "moe_sinkhorn: logits must be fp16/bf16/fp32");
       }
+      if (!(probe && rc == MOE_ERR_UNSUPPORTED)) return rc;
     }
   }
 
