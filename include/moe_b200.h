@@ -12,7 +12,13 @@
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it;
  *   - element type codes: MOE_F16, MOE_BF16, MOE_F32;
  *   - the library keeps no mutable global state: calls on different streams
- *     with different workspaces are independent.
+ *     with different workspaces are independent (moe_pack_static, which owns
+ *     its scratch, says what it shares);
+ *   - environment switches, read once per process, all default to the fast
+ *     path: MOE_B200_PDL=0 (no programmatic dependent launch between the
+ *     route kernels), MOE_B200_FUSED=1 (single-launch route), MOE_B200_M64=0
+ *     and MOE_B200_PAIR=0 (grouped GEMM: 128-row tiles only / single-tile
+ *     work units), MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
  *
  * Each declaration names the piece of the reference (path:lines inside
  * santiweide/moe-routers) that it replaces.
