@@ -22,8 +22,9 @@
 // pipe).  Both accumulators then belong to the same unit, so the epilogue overlaps the next unit's
 // main loop only from its second half on.  An expert with an odd number of tiles ends with a
 // single-tile unit.
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4)..).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4)..; the two warps of a lane quarter split
+// the tile's columns).
 //
 // Scattered output (`c_rows`): instead of row r of a dense C, every output row goes to its own base
 // address, which may lie in another GPU's memory (a peer mapping).  The expert-parallel layer uses
@@ -44,7 +45,7 @@ using namespace sm100;
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kUK = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
 constexpr int kABytes = kBM * kBK * 2;
 constexpr int kMaxStages = 8;
 constexpr int kMaxExperts = 1024;
@@ -251,7 +252,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, 128);
+      mbar_init(tempty0 + 8 * b, kThreads - 64);  // every epilogue thread arrives
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -375,7 +376,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncwarp();
   } else {
     // ------------------------------ epilogue -----------------------------------
-    const int q = warp & 3;
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    // Two warps share a lane quarter and split the tile's columns (dense output, >= 64 columns);
+    // otherwise the second warp of a quarter only takes part in the barriers.
+    const bool split = p.c_rows == nullptr && (swiglu ? BN / 2 : BN) >= 64;
+    const int col_half = (warp - 2) >> 2;   // 0: warps 2..5, 1: warps 6..9
     int local = 0;
     const int out_bn = swiglu ? BN / 2 : BN;  // output columns per tile
     bool ok = true;
@@ -392,7 +397,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int row0 = u.row0 + h * kBM;
         if (!mbar_wait(tfull0 + 8 * ab, par, p.status, 3)) { ok = false; break; }
         tc_fence_after();
-        if (h == 0 || u.two) {  // (the second accumulator of a single-tile unit holds nothing)
+        const int c_lo = split ? col_half * (out_bn / 2) : 0;
+        const int c_hi = split ? c_lo + out_bn / 2 : (col_half == 0 ? out_bn : 0);
+        if ((h == 0 || u.two) && c_lo < c_hi) {  // (the second accumulator of a single-tile unit holds nothing)
           int trow = q * 32 + lane;  // row of the tile held by this thread's TMEM lane
           bool lane_used = true;
           if (p.m64 && seg_end - row0 <= 64) {
@@ -410,7 +417,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (p.c_rows != nullptr && out_bn % 64 == 0) {
             uint8_t* stage = s_stage + q * kStageWarpBytes;
             uint16_t* mine = reinterpret_cast<uint16_t*>(stage + lane * kStageRowBytes);
-            for (int c0 = 0; c0 < out_bn; c0 += 64) {
+            for (int c0 = c_lo; c0 < c_hi; c0 += 64) {
 #pragma unroll
               for (int hh = 0; hh < 64; hh += 32)
                 epilogue_chunk<32>(acc + (uint32_t)(c0 + hh), acc + (uint32_t)(out_bn + c0 + hh), swiglu, p.act, scale,
@@ -420,13 +427,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               store_staged_rows(stage, crow, valid, c0, lane);
               __syncwarp();
             }
-          } else if (out_bn % 32 == 0) {
-            for (int c0 = 0; c0 < out_bn; c0 += 32)
+          } else if (out_bn % 64 == 0 || (!split && out_bn % 32 == 0)) {
+            for (int c0 = c_lo; c0 < c_hi; c0 += 32)
               epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid,
                                  crow + c0, brow ? brow + c0 : nullptr,
                                  (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
           } else {
-            for (int c0 = 0; c0 < out_bn; c0 += 16)
+            for (int c0 = c_lo; c0 < c_hi; c0 += 16)
               epilogue_chunk<16>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid,
                                  crow + c0, brow ? brow + c0 : nullptr,
                                  (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
