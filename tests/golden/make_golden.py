@@ -57,7 +57,7 @@ def gen_inputs(seed: int, t: int, d: int, e: int, dtype=torch.float32):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of santiweide/moe-routers to import the routers from")
     args = ap.parse_args()
     dm, br = import_reference(args.reference)
     torch.set_num_threads(4)
