@@ -55,6 +55,20 @@ def test_argument_errors_do_not_launch(lib):
     assert rc == 1
     with pytest.raises(lib.MoeError):
         lib.check(rc)
+    # the expert-parallel entry points validate before they touch the device
+    rc = L.moe_pack_scatter_to(None, 2, None, 4, 8, 64, 2, None, None, None, None, None, None, 0, None)
+    assert rc == 1 and "seg_base" in lib.last_error()
+    rc = L.moe_grouped_gemm_rows(None, None, None, None, 4, 16, 64, 64, lib.MOE_W_NK, 0, lib.MOE_ACT_NONE, None, None,
+                                 lib.MOE_F16, 0, None, 0, None)
+    assert rc == 1 and "row table" in lib.last_error()
+    rc = L.moe_ep_row_targets(None, None, 6, 4, 0, 64, 2, None, None)
+    assert rc == 1 and "divisible" in lib.last_error()
+    rc = L.moe_ep_segment_bases(None, None, 8, 4, 5, 64, 2, None, None, None)
+    assert rc == 1 and "rank" in lib.last_error()
+    rc = L.moe_ep_segment_bases(None, None, 8, 4, 0, 3, 2, None, None, None)
+    assert rc == 1 and "16 bytes" in lib.last_error()
+    assert L.moe_grouped_gemm(None, None, None, None, 4, 0, 64, 64, lib.MOE_W_NK, 0, lib.MOE_ACT_NONE, None, None,
+                              lib.MOE_F16, 0, None, 0, None) == 0  # zero rows: nothing to do
     # zero tokens is a valid no-op that needs no pointers
     assert L.moe_topk_select(None, lib.MOE_F16, 0, 64, 2, None, None, None) == 0
     assert L.moe_combine(None, lib.MOE_F16, None, None, 0, 8, 2, None, None) == 0
