@@ -16,7 +16,7 @@
  *     its scratch, says what it shares);
  *   - environment switches, read once per process, all default to the fast
  *     path: MOE_B200_PDL=0 (no programmatic dependent launch between the
- *     route kernels), MOE_B200_FUSED=1 (single-launch route), MOE_B200_M64=0
+ *     route kernels; moe_set_pdl changes it at run time), MOE_B200_M64=0
  *     and MOE_B200_PAIR=0 (grouped GEMM: 128-row tiles only / single-tile
  *     work units), MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
  *
@@ -64,6 +64,23 @@ size_t moe_workspace_bytes(int tokens, int experts, int top_k);
 /* Zero the status block of a workspace (async on `stream`).  Call once after
  * allocating the workspace. */
 int moe_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Limit, in nanoseconds, of every bounded device-side wait of kernels that are given this workspace
+ * (mbarrier waits, grid barriers, moe_ep_wait); 0 restores the default of 2 s.  Stored in the status
+ * block by an async copy on `stream`; call it outside stream capture.  A wait that runs out records
+ * a code in the status block (see moe_read_status) and the kernel returns; nothing traps.
+ * (Setup helper; the reference has no counterpart: its kernels never wait.) */
+int moe_set_wait_limit(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream);
+
+/* Kernel launches this library has issued in this process so far (all threads, captured launches
+ * count when they are captured).  Measurement helper; no counterpart in the reference. */
+long long moe_launch_count(void);
+
+/* Programmatic dependent launch between the kernels of a route (the scatter may start its input
+ * prefetch under the router kernel's epilogue): 0 = plain stream order, non-zero = on (default,
+ * unless MOE_B200_PDL=0 is in the environment).  Process-wide; takes effect for launches issued
+ * after the call.  Measurement helper; no counterpart in the reference. */
+int moe_set_pdl(int enabled);
 
 /* Copy the status block's first word to the host.  THIS CALL SYNCHRONISES
  * `stream`.  0 means no kernel recorded an error; otherwise the value encodes
@@ -303,6 +320,28 @@ int moe_ipc_close(void* base);
 
 int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts, int world,
                 int rank, int combine, int d, int elem_bytes, int32_t* local_offsets, void* stream);
+
+/*
+ * Rank-to-rank signals over peer mappings: the phase ordering of the expert-parallel layer without
+ * a collective.  Replaces: the all_to_all_single of the split sizes with its `.tolist()` host read and
+ * the implicit ordering of the blocking collectives (bench_2gpu_pcie.py:460-494).
+ *   Every rank owns a flag table int32 [slots][world], zero at start, in memory the peers have mapped.
+ *   moe_ep_signal: first copies `payload` (NULL, or `payload_words` int32 on this device, e.g. the
+ *     per-expert counts) to peer_payload[p] + payload_offset_words for every rank p, then makes all
+ *     earlier stores of this rank visible system-wide and stores `value` into entry [slot][rank] of
+ *     every rank's table (peer_flags: DEVICE array of `world` table addresses; own entry = own table).
+ *   moe_ep_wait: polls this rank's OWN table until every entry of `slot` has reached `value`
+ *     (signed distance, so the counter may wrap).  Bounded by the workspace's wait limit
+ *     (moe_set_wait_limit, default 2 s): on expiry the status block gets code 0x400 | rank-that-never-
+ *     signalled and the kernel returns.
+ *   Values must grow from call to call (pass a call counter); tables are never cleared.
+ *   One process per GPU: a waiting kernel and the kernels that signal it must run on different GPUs
+ *   (or the signals must already be in memory); two such kernels on one GPU may never overlap.
+ */
+int moe_ep_signal(void* const* peer_flags, int world, int rank, int slot, int value, const int32_t* payload,
+                  void* const* peer_payload, size_t payload_offset_words, int payload_words, void* stream);
+int moe_ep_wait(const int32_t* flags, int world, int slot, int value, void* workspace, size_t workspace_bytes,
+                void* stream);
 
 /*
  * Dispatch destinations: seg_base[g] (g = global expert) = address, inside inbox_bufs[owner of g]

@@ -28,6 +28,9 @@ SIGNATURES = {
     "moe_workspace_bytes": (_sz, [_i, _i, _i]),
     "moe_workspace_init": (_i, [_p, _sz, _p]),
     "moe_read_status": (_i, [_p, _p, C.POINTER(C.c_int)]),
+    "moe_set_wait_limit": (_i, [_p, _sz, C.c_ulonglong, _p]),
+    "moe_launch_count": (C.c_longlong, []),
+    "moe_set_pdl": (_i, [_i]),
     "moe_topk_select": (_i, [_p, _i, _i, _i, _i, _p, _p, _p]),
     "moe_pack": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "moe_fused_select": (_i, [_p, _i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
@@ -41,6 +44,8 @@ SIGNATURES = {
     "moe_ipc_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "moe_ipc_close": (_i, [_p]),
     "moe_ep_push": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]),
+    "moe_ep_signal": (_i, [_p, _i, _i, _i, _i, _p, _p, _sz, _i, _p]),
+    "moe_ep_wait": (_i, [_p, _i, _i, _i, _p, _sz, _p]),
     "moe_sinkhorn": (_i, [_p, _i, _i, _i, _i, _i, _f, _f, _p, _p, _p, _sz, _p]),
     "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),
     "moe_grouped_gemm_rows": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),

@@ -11,10 +11,15 @@ Per strategy, per iteration (forward only), times in microseconds, max over rank
                  are copied by the dispatch itself (T_comm) and T_route is GEMM + select + pack plan
     T_comm       dispatch + combine exchanges, run alone
     T_comp       expert FFN on own rows + on received rows (with re-bucketing), run alone
-    T_layer(seq) the whole layer with every stage on one stream
-    T_layer(ovl) the whole layer with the exchanges on a second stream
+    T_layer(seq) the whole layer as a serial chain: local pack, dispatch exchange, rank sync, expert FFN,
+                 combine exchange, rank sync, gate-weighted sum (peer transport: separate push kernels;
+                 nccl transport: every stage on one stream)
+    T_layer(ovl) the whole layer with the exchanges overlapped with compute (peer transport: the pack
+                 stores into the owners' inboxes and the second expert GEMM stores its rows into their
+                 home slots, tile by tile; nccl transport: exchanges on a second stream)
     T_layer(b2b) the layer called `iters` times back to back, per call (no host sync in between)
-    eta_overlap  (T_route + T_comm + T_comp + T_combine) / T_layer(ovl)      (bench_2gpu_pcie.py:586)
+    eta_overlap  (T_route + T_comm + T_comp + T_combine) / T_layer(ovl)      (bench_2gpu_pcie.py:586);
+                 eta_seq_over_overlap = T_layer(seq) / T_layer(ovl) compares the two executions directly
     load max/mean and CV of the per-expert route counts over all ranks       (:446-457)
 Each expert is a 2-layer GELU FFN d_model -> hidden -> d_model with N(0, 1/fan_in) weights.
 """
@@ -47,12 +52,13 @@ def run(args) -> list[dict]:
     if e % world != 0:
         raise ValueError("experts must be divisible by world_size")
     el = e // world
+    dtype = {"fp16": torch.float16, "bf16": torch.bfloat16}[getattr(args, "dtype", "fp16")]
     g = torch.Generator(device=dev).manual_seed(0)  # router and expert weights: same seed on every rank
-    w_router = (torch.randn(e, d, device=dev, generator=g) / d ** 0.5).half()
+    w_router = (torch.randn(e, d, device=dev, generator=g) / d ** 0.5).to(dtype)
     gl = torch.Generator(device=dev).manual_seed(1000 + rank)
-    w1 = (torch.randn(el, h, d, device=dev, generator=gl) / d ** 0.5).half()
-    w2 = (torch.randn(el, d, h, device=dev, generator=gl) / h ** 0.5).half()
-    x = torch.randn(t, d, device=dev, generator=gl).half()  # tokens differ per rank
+    w1 = (torch.randn(el, h, d, device=dev, generator=gl) / d ** 0.5).to(dtype)
+    w2 = (torch.randn(el, d, h, device=dev, generator=gl) / h ** 0.5).to(dtype)
+    x = torch.randn(t, d, device=dev, generator=gl).to(dtype)  # tokens differ per rank
 
     strategies = ["naive_topk", "fused_select", "sinkhorn"] if args.all_strategies else (args.strategies or [args.strategy])
     results = []
@@ -78,9 +84,10 @@ def run(args) -> list[dict]:
             o = out["o"]
             if transport == "peer":
                 pr = layer._peer
-                counts_all = torch.empty((world, e), dtype=torch.int32, device=dev)
-                dist.all_gather_into_tensor(counts_all, o["counts"])
-                y_packed = pr["y_home"]
+                layer._calls += 1
+                call = layer._calls
+                counts_all = layer.exchange_counts_peer(o["counts"], call)
+                y_packed = pr["y_home"][:x.size(0) * k]
 
                 fused = layer.fuse_combine
                 targets = layer._row_targets(counts_all) if fused else None
@@ -90,10 +97,10 @@ def run(args) -> list[dict]:
                         layer.dispatch_direct(x, o, counts_all)
                     else:
                         layer._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
-                    layer._rank_sync()
+                    layer._rank_sync(1, call)
                     if not fused:
                         layer._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
-                    layer._rank_sync()
+                    layer._rank_sync(2, call)
 
                 def comp():
                     layer._ffn(pr["inbox"], pr["offsets"], None if fused else pr["yb"], out_rows=targets)
@@ -139,6 +146,7 @@ def run(args) -> list[dict]:
             t_route_us=t_route, t_comm_us=t_comm, t_comp_us=t_comp, t_combine_us=t_combine,
             t_layer_seq_us=t_seq, t_layer_overlap_us=t_ovl, t_layer_back_to_back_us=t_b2b,
             eta_overlap=(t_route + t_comm + t_comp + t_combine) / max(t_ovl, 1e-6),
+            eta_seq_over_overlap=t_seq / max(t_ovl, 1e-6),
             load_max_over_mean=float(counts.max() / (mean + 1e-9)),
             load_cv=float(counts.std(unbiased=False) / (mean + 1e-9)),
             transport=transport, direct_dispatch=bool(layer.direct_dispatch) if transport == "peer" else None,
@@ -152,7 +160,7 @@ def run(args) -> list[dict]:
 
 def main() -> None:
     p = argparse.ArgumentParser()
-    p.add_argument("--dtype", type=str, default="fp16", choices=["fp16"])
+    p.add_argument("--dtype", type=str, default="fp16", choices=["fp16", "bf16"])
     p.add_argument("--tokens", type=int, default=4096, help="T (tokens per rank)")
     p.add_argument("--d_model", type=int, default=4096)
     p.add_argument("--hidden", type=int, default=8192)

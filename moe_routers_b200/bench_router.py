@@ -22,6 +22,8 @@ import torch
 from . import ops
 from .strategies import STRATEGIES, route
 
+_DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
 
 def _cuda_time(fn) -> float:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -34,54 +36,95 @@ def _cuda_time(fn) -> float:
 
 def _torch_pack(x, topk_idx):
     """The reference's sorted pack (bench_router.py:57-78) in torch ops, without the gate multiply:
-    the comparison leg of the permutation sweep."""
+    a comparison leg of the permutation sweep."""
     s_, k_ = topk_idx.shape
     token_ids = torch.arange(s_, device=x.device, dtype=torch.int64).unsqueeze(1).expand(s_, k_).reshape(-1)
     sort_idx = torch.argsort(topk_idx.reshape(-1).to(torch.int64))
     return x.index_select(0, token_ids).index_select(0, sort_idx)
 
 
-def run_perm_sweep(args) -> None:
-    """Permutation latency against batch size with the DRAM-limit model of bench_router.py:284-388:
-    random uniform routes, t_theory = 2 * R * d * elem / peak (the reference's "ideal one pass";
-    the compulsory traffic (1 + k) * T * d * elem is reported beside it)."""
+def _torch_pack_mask_scan(x, topk_idx, n_experts: int):
+    """The reference's deliberately naive pack (bench_router.py:81-120): replicate every token once per
+    pick, then one boolean-mask pass over all routes per expert and a final concatenation.  Baseline
+    leg of the permutation sweep (`t_perm_naive_ms`); torch ops, as in the reference."""
+    s_, k_ = topk_idx.shape
+    flat_e = topk_idx.reshape(-1).to(torch.int64)
+    rows = x.repeat_interleave(k_, dim=0)
+    parts = [rows[flat_e == ex] for ex in range(int(n_experts))]
+    return torch.cat(parts, dim=0) if parts else rows[:0]
+
+
+PERM_SWEEP_FIELDS = ["batch_size", "seq_len", "tokens", "experts", "top_k", "d_model", "dtype", "t_perm_naive_ms",
+                     "t_perm_sorted_ms", "t_theory_ms", "peak_bw_gbs", "sorted_achieved_bw_gbs",
+                     # beyond the reference's columns (bench_router.py:303-316):
+                     "t_perm_torch_sorted_ms", "compulsory_bytes"]
+
+
+def perm_model(tokens: int, top_k: int, d_model: int, elem_bytes: int, peak_bw_gbs: float, t_sorted_ms: float):
+    """The reference's DRAM-limit model of a pack (bench_router.py:355-358): one pass reads and writes
+    every routed row, ideal_bytes = 2 * R * d * elem with R = tokens * top_k; t_theory = ideal_bytes /
+    peak; achieved = ideal_bytes / measured time.  `compulsory_bytes` is the smaller traffic a pack
+    that reads each token once really needs, (1 + k) * T * d * elem.  Returns a dict of the derived
+    CSV columns."""
+    routes = tokens * top_k
+    ideal = 2.0 * routes * d_model * elem_bytes
+    if peak_bw_gbs is None or peak_bw_gbs <= 0:
+        t_theory, achieved = float("nan"), float("nan")
+    else:
+        t_theory = ideal / (peak_bw_gbs * 1e9) * 1e3
+        achieved = ideal / (t_sorted_ms * 1e-3) / 1e9 if t_sorted_ms > 0 else float("nan")
+    return dict(t_theory_ms=t_theory, sorted_achieved_bw_gbs=achieved,
+                compulsory_bytes=(1 + top_k) * tokens * d_model * elem_bytes)
+
+
+def write_perm_csv(path: str, rows: list) -> None:
     import csv
 
+    with open(path, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=PERM_SWEEP_FIELDS)
+        w.writeheader()
+        w.writerows(rows)
+
+
+def run_perm_sweep(args) -> None:
+    """Permutation latency against batch size with the DRAM-limit model of bench_router.py:284-388:
+    random uniform routes; per batch size the naive mask-scan pack (torch), the reference's sorted
+    pack (torch) and this library's pack kernel, next to t_theory = 2 * R * d * elem / peak."""
     dev = torch.device("cuda")
     torch.manual_seed(0)
     bw = float(args.peak_bw_gbs) if args.peak_bw_gbs is not None else 6548.8
+    dtype = _DTYPES[args.dtype]
     e, k, d = args.experts, args.top_k, args.d_model
+    n = max(args.iters, 1)
     rows = []
     for bsz in args.batch_sizes:
         tokens = int(bsz) * int(args.seq_len)
-        x = torch.randn(tokens, d, device=dev).half()
+        x = torch.randn(tokens, d, device=dev).to(dtype)
         idx = torch.randint(0, e, (tokens, k), device=dev, dtype=torch.int32)
         for _ in range(args.warmup):
             ops.pack(x, idx, e)
             _torch_pack(x, idx)
-        t_ours = sum(_cuda_time(lambda: ops.pack(x, idx, e)) for _ in range(args.iters)) / max(args.iters, 1)
-        t_torch = sum(_cuda_time(lambda: _torch_pack(x, idx)) for _ in range(args.iters)) / max(args.iters, 1)
-        routes = tokens * k
-        ideal = 2.0 * routes * d * 2
-        rows.append(dict(batch_size=int(bsz), seq_len=int(args.seq_len), tokens=tokens, experts=e, top_k=k, d_model=d,
-                         dtype="float16", t_perm_naive_ms=t_torch, t_perm_sorted_ms=t_ours,
-                         t_theory_ms=ideal / (bw * 1e9) * 1e3, peak_bw_gbs=bw,
-                         sorted_achieved_bw_gbs=ideal / (t_ours * 1e-3) / 1e9,
-                         compulsory_bytes=(1 + k) * tokens * d * 2))
-    with open(args.csv_out, "w", newline="") as f:
-        w = csv.DictWriter(f, fieldnames=list(rows[0].keys()))
-        w.writeheader()
-        w.writerows(rows)
+            _torch_pack_mask_scan(x, idx, e)
+        t_ours = sum(_cuda_time(lambda: ops.pack(x, idx, e)) for _ in range(n)) / n
+        t_torch = sum(_cuda_time(lambda: _torch_pack(x, idx)) for _ in range(n)) / n
+        t_naive = sum(_cuda_time(lambda: _torch_pack_mask_scan(x, idx, e)) for _ in range(n)) / n
+        row = dict(batch_size=int(bsz), seq_len=int(args.seq_len), tokens=tokens, experts=e, top_k=k, d_model=d,
+                   dtype=str(dtype).replace("torch.", ""), t_perm_naive_ms=t_naive, t_perm_sorted_ms=t_ours,
+                   t_perm_torch_sorted_ms=t_torch, peak_bw_gbs=bw)
+        row.update(perm_model(tokens, k, d, x.element_size(), bw, t_ours))
+        rows.append(row)
+    write_perm_csv(args.csv_out, rows)
     print("perm_sweep: wrote CSV:", args.csv_out)
     for r in rows:
-        print(f"B={r['batch_size']:<4d} tokens={r['tokens']:<6d} torch {r['t_perm_naive_ms'] * 1e3:8.1f} us  "
-              f"ours {r['t_perm_sorted_ms'] * 1e3:8.1f} us  theory {r['t_theory_ms'] * 1e3:7.1f} us")
+        print(f"B={r['batch_size']:<4d} tokens={r['tokens']:<6d} naive {r['t_perm_naive_ms'] * 1e3:9.1f} us  "
+              f"torch sorted {r['t_perm_torch_sorted_ms'] * 1e3:8.1f} us  ours {r['t_perm_sorted_ms'] * 1e3:8.1f} us  "
+              f"theory {r['t_theory_ms'] * 1e3:7.1f} us")
 
 
 def main() -> None:
     p = argparse.ArgumentParser()
     p.add_argument("--device", type=str, default="cuda")
-    p.add_argument("--dtype", type=str, default="fp16", choices=["fp16"])
+    p.add_argument("--dtype", type=str, default="fp16", choices=["fp16", "bf16"])
     p.add_argument("--tokens", type=int, default=4096)
     p.add_argument("--d_model", type=int, default=4096)
     p.add_argument("--experts", type=int, default=64)
@@ -113,8 +156,9 @@ def main() -> None:
 
     torch.manual_seed(0)
     dev = torch.device("cuda")
-    x = torch.randn(args.tokens, args.d_model, device=dev).half()
-    w = (torch.randn(args.experts, args.d_model, device=dev) / args.d_model ** 0.5).half()
+    dtype = _DTYPES[args.dtype]
+    x = torch.randn(args.tokens, args.d_model, device=dev).to(dtype)
+    w = (torch.randn(args.experts, args.d_model, device=dev) / args.d_model ** 0.5).to(dtype)
     strategies = STRATEGIES if args.all_strategies else (args.strategies or [args.strategy])
     unknown = [s for s in strategies if s not in STRATEGIES]
     if unknown:
@@ -148,8 +192,8 @@ def main() -> None:
         from .strategies import masked_matmul_forward, moe_forward
 
         h = args.hidden
-        w1 = (torch.randn(e, h, args.d_model, device=dev) / args.d_model ** 0.5).half()
-        w2 = (torch.randn(e, args.d_model, h, device=dev) / h ** 0.5).half()
+        w1 = (torch.randn(e, h, args.d_model, device=dev) / args.d_model ** 0.5).to(dtype)
+        w2 = (torch.randn(e, args.d_model, h, device=dev) / h ** 0.5).to(dtype)
 
         def layer_once(strategy):
             r = route(strategy, x, w, k, sinkhorn_iters=args.sinkhorn_iters,
@@ -166,7 +210,7 @@ def main() -> None:
             layer_ms[s] = sum(_cuda_time(lambda: layer_once(s)) for _ in range(args.iters)) / max(args.iters, 1)
 
     print("strategies:", strategies)
-    print("device:", dev, "dtype: torch.float16")
+    print("device:", dev, "dtype:", dtype)
     print("T(tokens):", args.tokens, "d_model:", args.d_model, "E:", e, "k:", k)
     print("skew_experts:", args.skew_experts, "skew_bias:", args.skew_bias)
     print("")

@@ -1,5 +1,7 @@
 // Library-level entry points: version, error text, workspace helpers.
+#include <atomic>
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -23,15 +25,53 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static std::atomic<long long> g_launches{0};
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 int check_launch(const char* what) {
   const cudaError_t e = cudaGetLastError();
-  if (e == cudaSuccess) return MOE_OK;
+  if (e == cudaSuccess) {
+    note_launch();
+    return MOE_OK;
+  }
   return fail(MOE_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// -1: not decided yet (the environment decides on first use), 0 / 1: off / on
+static std::atomic<int> g_pdl{-1};
+
+bool pdl_enabled() {
+  int v = g_pdl.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* env = getenv("MOE_B200_PDL");
+    v = (env && env[0] == '0') ? 0 : 1;
+    g_pdl.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
 }
 
 }  // namespace moe
 
-extern "C" int moe_version(void) { return 100; }
+extern "C" int moe_version(void) { return 200; }
+
+extern "C" long long moe_launch_count(void) { return moe::g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int moe_set_pdl(int enabled) {
+  moe::g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  return MOE_OK;
+}
+
+extern "C" int moe_set_wait_limit(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream) {
+  using namespace moe;
+  if (!workspace || workspace_bytes < (size_t)(kStatusBytes + kControlBytes))
+    return fail(MOE_ERR_WORKSPACE, "moe_set_wait_limit: workspace too small");
+  // the value travels by value inside the launch of a tiny memcpy node: no host buffer has to outlive the call
+  const cudaError_t e = cudaMemcpyAsync(static_cast<char*>(workspace) + 2 * sizeof(int32_t), &limit_ns, sizeof(limit_ns),
+                                        cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_set_wait_limit: %s", cudaGetErrorString(e));
+  return MOE_OK;
+}
 
 extern "C" const char* moe_last_error(void) { return moe::g_error; }
 
@@ -63,6 +103,7 @@ extern "C" int moe_read_status(const void* workspace, void* stream, int* status_
     const char* what = (v & 0xf00) == kErrMbarTimeout   ? "an mbarrier wait gave up"
                        : (v & 0xf00) == kErrGridBarrier ? "a grid barrier wait gave up"
                        : (v & 0xf00) == kErrBadIndex    ? "an expert index was out of range"
+                       : (v & 0xf00) == kErrPeerWait    ? "a wait for a peer rank's signal gave up"
                                                         : "unknown device error";
     return fail(MOE_ERR_DEVICE, "device status 0x%x: %s", v, what);
   }

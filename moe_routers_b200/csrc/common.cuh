@@ -13,7 +13,8 @@
 namespace moe {
 
 // ---- workspace layout -------------------------------------------------------
-// [0, 256)            status block: int32 words, word 0 = first recorded error
+// [0, 256)            status block: int32 words, word 0 = first recorded error; words 2..3 = limit of
+//                     every bounded device-side wait in nanoseconds as one uint64 (0 = the default)
 // [256, 512)          control block: tickets / barrier counters (self-resetting)
 // [512, ...)          tile histograms  int32 [num_tiles][experts]
 //                     tile bases       int32 [num_tiles][experts]
@@ -27,6 +28,7 @@ constexpr int kMaxGridBlocks = 256;  // upper bound of the co-resident grid of t
 constexpr int kErrMbarTimeout = 0x100;   // | role id
 constexpr int kErrGridBarrier = 0x200;
 constexpr int kErrBadIndex = 0x300;
+constexpr int kErrPeerWait = 0x400;      // | rank that never signalled
 
 struct Workspace {
   int32_t* status;
@@ -63,7 +65,9 @@ inline Workspace carve(void* ws, int tokens, int experts) {
 // ---- error text (thread local, host) ---------------------------------------
 void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
-int check_launch(const char* what);
+int check_launch(const char* what);  // counts the launch when it succeeded
+void note_launch();                  // for launches checked by hand (cudaLaunchKernelEx)
+bool pdl_enabled();                  // programmatic dependent launch between the route kernels
 
 __device__ __forceinline__ void record_error(int32_t* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);

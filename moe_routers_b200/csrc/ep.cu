@@ -10,7 +10,7 @@
 // every CTA recomputes the few prefix sums it needs (world * local_experts <= 1024 values).
 #include <cstring>
 
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace moe {
 namespace {
@@ -276,6 +276,7 @@ extern "C" int moe_ep_push(const void* local, void* const* peer_bufs, const int3
   if (d <= 0 || (elem_bytes != 2 && elem_bytes != 4) || ((size_t)d * elem_bytes) % 16 != 0)
     return fail(MOE_ERR_ARG, "moe_ep_push: rows must be a multiple of 16 bytes");
   if (!local || !peer_bufs || !counts_all) return fail(MOE_ERR_ARG, "moe_ep_push: null pointer");
+  if ((reinterpret_cast<uintptr_t>(local) & 15) != 0) return fail(MOE_ERR_ARG, "moe_ep_push: local must be 16-byte aligned");
   dim3 grid(experts, 8, 1);  // world * (experts / world) segments, 8 CTAs each
   ep_push_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const char*>(local), reinterpret_cast<char* const*>(peer_bufs), counts_all, experts, world, rank,
@@ -312,6 +313,92 @@ extern "C" int moe_ep_segment_bases(void* const* inbox_bufs, const int32_t* coun
       reinterpret_cast<char* const*>(inbox_bufs), counts_all, experts, world, rank, (size_t)d * elem_bytes,
       reinterpret_cast<char**>(seg_base), local_offsets);
   return check_launch("ep_segment_bases_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Rank-to-rank signals over the peer mappings: the phase ordering of the expert-parallel layer
+// without a collective.  Every rank owns a flag table int32 [slots][world] in memory its peers have
+// mapped; `signal` stores `value` into entry [slot][my rank] of every rank's table (after an optional
+// small payload, e.g. the per-expert counts, into every rank's payload buffer), `wait` polls the
+// rank's OWN table until all entries of the slot have reached `value`.  Values only grow (the
+// caller passes its call counter), so a table never has to be cleared.  The wait is bounded in
+// time like every other device-side wait of the library.
+namespace moe {
+namespace {
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kThreads)
+ep_signal_kernel(int32_t* const* __restrict__ peer_flags, int world, int rank, int slot, int32_t value,
+                 const int32_t* __restrict__ payload, int32_t* const* __restrict__ peer_payload,
+                 size_t payload_offset_words, int payload_words) {
+  if (payload != nullptr) {
+    for (int i = threadIdx.x; i < payload_words * world; i += kThreads) {
+      const int p = i / payload_words, j = i - p * payload_words;
+      peer_payload[p][payload_offset_words + j] = payload[j];
+    }
+  }
+  // everything this rank stored before (earlier kernels of the stream included) becomes visible to
+  // the peers before the flag does
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < world) st_release_sys(peer_flags[threadIdx.x] + (size_t)slot * world + rank, value);
+}
+
+__global__ void __launch_bounds__(32)
+ep_wait_kernel(const int32_t* __restrict__ flags, int world, int slot, int32_t value, int32_t* status) {
+  const int32_t* mine = flags + (size_t)slot * world;
+  for (int p = threadIdx.x; p < world; p += 32) {
+    bool seen = false;
+#pragma unroll 1
+    for (int i = 0; i < 4096 && !seen; ++i) seen = ld_acquire_sys(mine + p) - value >= 0;
+    if (!seen) {
+      const unsigned long long t0 = sm100::globaltimer_ns();
+      const unsigned long long limit = sm100::wait_limit_ns(status);
+      while (!seen) {
+#pragma unroll 1
+        for (int i = 0; i < 256 && !seen; ++i) seen = ld_acquire_sys(mine + p) - value >= 0;
+        if (!seen && sm100::globaltimer_ns() - t0 > limit) {
+          record_error(status, kErrPeerWait | (p & 0xff));
+          break;
+        }
+      }
+    }
+  }
+  __threadfence_system();
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_ep_signal(void* const* peer_flags, int world, int rank, int slot, int value, const int32_t* payload,
+                             void* const* peer_payload, size_t payload_offset_words, int payload_words, void* stream) {
+  using namespace moe;
+  if (world <= 0 || world > kThreads || rank < 0 || rank >= world || slot < 0)
+    return fail(MOE_ERR_ARG, "moe_ep_signal: bad world / rank / slot");
+  if (!peer_flags) return fail(MOE_ERR_ARG, "moe_ep_signal: null flag table");
+  if (payload != nullptr && (!peer_payload || payload_words <= 0)) return fail(MOE_ERR_ARG, "moe_ep_signal: bad payload");
+  ep_signal_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<int32_t* const*>(peer_flags), world, rank, slot, value, payload,
+      reinterpret_cast<int32_t* const*>(peer_payload), payload_offset_words, payload ? payload_words : 0);
+  return check_launch("ep_signal_kernel");
+}
+
+extern "C" int moe_ep_wait(const int32_t* flags, int world, int slot, int value, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  using namespace moe;
+  if (world <= 0 || slot < 0 || !flags) return fail(MOE_ERR_ARG, "moe_ep_wait: bad argument");
+  if (!workspace || workspace_bytes < (size_t)kStatusBytes) return fail(MOE_ERR_WORKSPACE, "moe_ep_wait: workspace missing");
+  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, slot, value,
+                                                                   static_cast<int32_t*>(workspace));
+  return check_launch("ep_wait_kernel");
 }
 
 extern "C" int moe_enable_peer_access(int peer_device) {

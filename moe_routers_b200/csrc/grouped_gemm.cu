@@ -474,6 +474,11 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
   if (rows == 0) return MOE_OK;
   if (!a || !w || (!c && !c_rows) || !offsets) return fail(MOE_ERR_ARG, "moe_grouped_gemm: null pointer");
   if (!workspace || workspace_bytes < (size_t)kStatusBytes) return fail(MOE_ERR_WORKSPACE, "moe_grouped_gemm: workspace missing");
+  // the epilogue stores 128-bit pieces; bias is read with 128-bit loads
+  if (c != nullptr && (reinterpret_cast<uintptr_t>(c) & 15) != 0)
+    return fail(MOE_ERR_ARG, "moe_grouped_gemm: c must be 16-byte aligned");
+  if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) != 0)
+    return fail(MOE_ERR_ARG, "moe_grouped_gemm: bias must be 16-byte aligned");
   const bool swiglu = activation == MOE_ACT_SWIGLU;
   const int n_w = swiglu ? 2 * N : N;  // output features held by one weight matrix
 

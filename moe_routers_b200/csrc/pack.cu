@@ -129,6 +129,9 @@ pack_scatter_kernel(const char* __restrict__ x, const int32_t* __restrict__ idx,
   const int t0 = tile * kTileTokens;
   const int tile_tokens = min(kTileTokens, tokens - t0);
 
+  // a kernel launched behind this one with programmatic stream serialisation (the next route's
+  // router GEMM) may set itself up as soon as every CTA of this grid is running
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   tile_destinations(idx, tile_hist, tile_base, counts, offsets, row_route, route_row, tile, t0,
                     tile_tokens * top_k, experts, top_k, num_tiles, blockIdx.x == 0, part == 0, s_base,
@@ -185,6 +188,9 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
   const int items = (packed != nullptr || seg_base != nullptr) ? tile_tokens * chunks : 0;
   const int depth = nbuf / kBulkIssuers;  // buffers owned by each issuing thread
 
+  // a kernel launched behind this one with programmatic stream serialisation (the next route's
+  // router GEMM) may set itself up as soon as every CTA of this grid is running
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int b = 0; b < nbuf; ++b)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(s_bar + b)) : "memory");
@@ -263,15 +269,6 @@ __global__ void pack_zero_kernel(int32_t* counts, int32_t* offsets, int experts)
   if (e <= experts) offsets[e] = 0;
 }
 
-// MOE_B200_PDL=0 in the environment turns programmatic dependent launch off (plain stream order).
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* v = getenv("MOE_B200_PDL");
-    return !(v && v[0] == '0');
-  }();
-  return on;
-}
-
 int pick_split(int num_tiles) {
   // aim for a few CTAs per SM (148 SMs) without dropping below one token per warp
   int split = 1;
@@ -338,6 +335,7 @@ int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int t
       err = cudaLaunchKernelEx(&cfg, pack_scatter_bulk_kernel, xs, idx, th, tile_base, counts, offsets, ps,
                                row_route, route_row, tokens, row_bytes, experts, top_k, nt, nbuf, chunk, st, sb);
       if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_bulk_kernel: %s", cudaGetErrorString(err));
+      note_launch();
       return MOE_OK;
     }
   }
@@ -356,6 +354,7 @@ int launch_scan_scatter(const void* x, int elem_bytes, const int32_t* idx, int t
   else MOE_SCATTER(uint16_t);
 #undef MOE_SCATTER
   if (err != cudaSuccess) return fail(MOE_ERR_LAUNCH, "pack_scatter_kernel: %s", cudaGetErrorString(err));
+  note_launch();
   return MOE_OK;
 }
 

@@ -81,17 +81,6 @@ __device__ __forceinline__ void topk_rows(const SParams& p, const float* s_k, co
   }
 }
 
-#ifdef MOE_SINKHORN_TRACE
-#define SK_TRACE(slot)                                                                  \
-  if (threadIdx.x == 0 && blockIdx.x == 0) {                                            \
-    long long t_;                                                                       \
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_)::"memory");                        \
-    reinterpret_cast<long long*>(p.scratch)[(slot)] = t_;                               \
-  }
-#else
-#define SK_TRACE(slot)
-#endif
-
 template <typename T, bool CLUSTER>
 __global__ void __launch_bounds__(CLUSTER ? 1024 : kThreads)
 sinkhorn_kernel(const SParams p) {
@@ -110,13 +99,13 @@ sinkhorn_kernel(const SParams p) {
   float* s_all = s_part + (size_t)groups * E;  // [2][nblk][E] partials of all CTAs (CLUSTER only)
   __shared__ int s_flag;
 
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
   const int row0 = blockIdx.x * R;
   const int nrows = max(0, min(R, p.tokens - row0));
   const T* logits = static_cast<const T*>(p.logits);
   const float ct = (float)p.tokens / (float)max(E, 1);
-  SK_TRACE(0);
+  // Remote shared-memory stores below need every CTA of the cluster to be running: arrive now, wait
+  // just before the first store (by then the others have long started, so the wait costs nothing).
+  if constexpr (CLUSTER) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
   // ---- K = exp(s - rowmax), s = (logits / temperature) rounded to the logits dtype ----
   // coalesced load of the CTA's rows, then one thread per row (rows are SK = E+1 floats apart, so
@@ -140,7 +129,6 @@ sinkhorn_kernel(const SParams p) {
 
   const int g = threadIdx.x / cw;
   const int jc = threadIdx.x % cw;
-  SK_TRACE(1);
 
   bool ok = true;
   for (int it = 0; it <= p.iters && ok; ++it) {
@@ -158,7 +146,6 @@ sinkhorn_kernel(const SParams p) {
       s_a[r] = a / (a * (s0 + s1) + p.eps);
     }
     __syncthreads();
-    SK_TRACE(2 + 4 * it);
     if (it == p.iters) break;  // the last pass is the final row normalisation only
 
     // ---- column step: b_j <- b_j * (T/E) / (b_j * sum_i a_i K_ij + eps) ----
@@ -170,10 +157,10 @@ sinkhorn_kernel(const SParams p) {
       }
     }
     __syncthreads();
-    SK_TRACE(3 + 4 * it);
     if constexpr (CLUSTER) {
       // this CTA's column sums go into slot [it & 1][my rank] of every CTA of the cluster
       const uint32_t me = sm100::cluster_ctarank();
+      if (it == 0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
       float* slot = s_all + ((size_t)(it & 1) * nblk + me) * E;
       for (int j = threadIdx.x; j < E; j += nthreads) {
         float s = 0.f;
@@ -182,7 +169,6 @@ sinkhorn_kernel(const SParams p) {
         for (int c = 0; c < nblk; ++c) sm100::st_cluster_f32(sm100::map_to_cta(local, (uint32_t)c), s);
       }
       sm100::cluster_sync_all();
-      SK_TRACE(4 + 4 * it);
       const float* all = s_all + (size_t)(it & 1) * nblk * E;
       for (int j = threadIdx.x; j < E; j += nthreads) {
         float s = 0.f;
@@ -191,7 +177,6 @@ sinkhorn_kernel(const SParams p) {
         s_b[j] = b / (b * s + p.eps) * ct;
       }
       __syncthreads();
-      SK_TRACE(5 + 4 * it);
     } else {
       float* mine = p.scratch + ((size_t)(it & 1) * nblk + blockIdx.x) * E;
       for (int j = threadIdx.x; j < E; j += nthreads) {
@@ -233,14 +218,12 @@ sinkhorn_kernel(const SParams p) {
     }
   }
   if (!ok) return;
-  SK_TRACE(60);
 
   // ---- top-k of q_ij = a_i K_ij b_j (lowest index wins ties), w = vals / (sum(vals) + eps) ----
   if (p.top_k <= 1) topk_rows<1>(p, s_k, s_a, s_b, SK, row0, nrows);
   else if (p.top_k <= 2) topk_rows<2>(p, s_k, s_a, s_b, SK, row0, nrows);
   else if (p.top_k <= 4) topk_rows<4>(p, s_k, s_a, s_b, SK, row0, nrows);
   else topk_rows<8>(p, s_k, s_a, s_b, SK, row0, nrows);
-  SK_TRACE(61);
 }
 
 constexpr int kClusterCtas = 8;        // portable cluster size
@@ -292,6 +275,7 @@ int launch_sinkhorn_cluster(SParams& p, int ctas, size_t smem, cudaStream_t s, b
   }
   e = cudaLaunchKernelEx(&cfg, sinkhorn_kernel<T, true>, p);
   if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "sinkhorn_kernel (cluster): %s", cudaGetErrorString(e));
+  note_launch();
   return MOE_OK;
 }
 
@@ -309,6 +293,7 @@ int launch_sinkhorn(SParams& p, int grid, size_t smem, cudaStream_t s) {
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(sinkhorn_kernel<T, false>), dim3(grid), dim3(kThreads), args, smem, s);
   if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "sinkhorn_kernel: %s", cudaGetErrorString(e));
+  note_launch();
   return MOE_OK;
 }
 

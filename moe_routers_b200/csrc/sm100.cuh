@@ -10,7 +10,7 @@
 namespace moe {
 namespace sm100 {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default limit of a wait: 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -20,6 +20,14 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// Limit of a bounded wait: the caller's setting in words 2..3 of the status block
+// (moe_set_wait_limit), else the default.  Only read on the slow path of a wait.
+__device__ __forceinline__ unsigned long long wait_limit_ns(const int32_t* status) {
+  if (status == nullptr) return kWaitLimitNs;
+  const unsigned long long v = *reinterpret_cast<const volatile unsigned long long*>(status + 2);
+  return v != 0ull ? v : kWaitLimitNs;
 }
 
 // ---- mbarrier ---------------------------------------------------------------
@@ -60,11 +68,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
   for (int i = 0; i < 2048; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
+  const unsigned long long limit = wait_limit_ns(status);
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > limit) {
       record_error(status, kErrMbarTimeout | code);
       return false;
     }
@@ -243,10 +252,11 @@ __device__ __forceinline__ bool grid_barrier(int32_t* control, int nblocks, int3
       for (int i = 0; i < 4096 && !released; ++i) released = ld_acquire_gpu(control + 1) != gen;
       if (!released) {
         const unsigned long long t0 = sm100::globaltimer_ns();
+        const unsigned long long limit = sm100::wait_limit_ns(status);
         while (!released) {
 #pragma unroll 1
           for (int i = 0; i < 1024 && !released; ++i) released = ld_acquire_gpu(control + 1) != gen;
-          if (!released && sm100::globaltimer_ns() - t0 > sm100::kWaitLimitNs) {
+          if (!released && sm100::globaltimer_ns() - t0 > limit) {
             record_error(status, kErrGridBarrier);
             ok = 0;
             break;
@@ -268,5 +278,8 @@ int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
                    uint32_t box_cols, uint32_t box_rows);
 int encode_tmap_3d(CUtensorMap* map, const void* base, uint64_t d2, uint64_t rows, uint64_t cols,
                    uint64_t row_stride_bytes, uint64_t d2_stride_bytes, uint32_t box_cols, uint32_t box_rows);
+
+int encode_tmap_4d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1,
+                   uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3);
 
 }  // namespace moe

@@ -84,7 +84,8 @@ class EPMoELayer:
 
     def __init__(self, w_router, w1_local, w2_local, top_k: int = 2, *, activation: str = "gelu",
                  strategy: str = "fused_select", sinkhorn_iters: int = 10, sinkhorn_temperature: float = 1.0,
-                 skew_experts: int = 0, skew_bias: float = 0.0, group=None, transport: str = "peer"):
+                 skew_experts: int = 0, skew_bias: float = 0.0, group=None, transport: str = "peer",
+                 max_tokens: Optional[int] = None):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -115,6 +116,12 @@ class EPMoELayer:
         # copy, no push kernel); False: pack locally, then push
         self.direct_dispatch = True
         self._peer = None
+        # peer transport: the inbox / result buffers are sized ONCE, at the first call (a collective
+        # set-up), for `max_tokens` tokens per rank (default: the first batch; ranks may differ, the
+        # largest counts); a later batch with more tokens is refused instead of re-sized, because a
+        # re-size decided by one rank alone would leave the others in a different collective
+        self.max_tokens = max_tokens
+        self._calls = 0
         self.comm_stream = torch.cuda.Stream()
         # Expert groups pipelined against the exchanges, and SMs the persistent GEMM leaves to the
         # exchange kernels while it runs.  Measured on 2 B200s (T=4096/rank, d=4096, h=8192, E=64):
@@ -247,16 +254,22 @@ class EPMoELayer:
 
     # ---- device-initiated transport ------------------------------------------------------------
     def _setup_peer(self, rows_home: int, d: int, dtype, device):
-        """Allocate this rank's inbox / result buffers and map every peer's into this process.
-        inbox: worst case all W * rows_home routes of the job land on this rank."""
+        """Allocate this rank's inbox / result / flag buffers and map every peer's into this process
+        (collective: every rank calls it once, at its first forward).  inbox: worst case all
+        W * max_rows routes of the job land on this rank."""
         import ctypes
 
         w = self.world
+        want = max(int(rows_home), int(self.max_tokens) * self.k if self.max_tokens is not None else 0)
         sizes = [None] * w
-        dist.all_gather_object(sizes, int(rows_home), group=self.group)
-        cap = w * max(sizes)  # ranks may hold different numbers of tokens
+        dist.all_gather_object(sizes, want, group=self.group)
+        max_rows = max(sizes)  # ranks may hold different numbers of tokens
+        cap = w * max_rows
         inbox = torch.empty((cap, d), dtype=dtype, device=device)
-        y_home = torch.empty((rows_home, d), dtype=dtype, device=device)
+        y_home = torch.empty((max_rows, d), dtype=dtype, device=device)
+        # rank-to-rank signals: flag table int32 [3 slots][W] and the counts of both call parities
+        # int32 [2][W][E] in one allocation the peers map
+        sync = torch.zeros(3 * w + 2 * w * self.e, dtype=torch.int32, device=device)
 
         def export(t):
             # (device, ipc handle of the allocation's base, size, offset of the storage in it, ...)
@@ -272,7 +285,8 @@ class EPMoELayer:
 
         gathered = [None] * w
         if w > 1:
-            dist.all_gather_object(gathered, (export(inbox), export(y_home)), group=self.group)
+            torch.cuda.synchronize(device)  # the flag table is zero before any peer can see it
+            dist.all_gather_object(gathered, (export(inbox), export(y_home), export(sync)), group=self.group)
         opened = {}  # one mapping per distinct allocation
 
         def map_peer(handle, offset):
@@ -283,31 +297,39 @@ class EPMoELayer:
                 opened[handle] = base.value
             return opened[handle] + offset
 
-        in_ptrs, home_ptrs = [], []
+        in_ptrs, home_ptrs, sync_ptrs = [], [], []
         for p_ in range(w):
             if p_ == self.rank:
                 in_ptrs.append(inbox.data_ptr())
                 home_ptrs.append(y_home.data_ptr())
+                sync_ptrs.append(sync.data_ptr())
             else:
-                (h_i, o_i), (h_h, o_h) = gathered[p_]
+                (h_i, o_i), (h_h, o_h), (h_s, o_s) = gathered[p_]
                 in_ptrs.append(map_peer(h_i, o_i))
                 home_ptrs.append(map_peer(h_h, o_h))
+                sync_ptrs.append(map_peer(h_s, o_s))
+        counts_base = 3 * w  # word offset of the counts inside `sync`
         self._peer = dict(
-            rows_home=rows_home, d=d, cap=cap, inbox=inbox, y_home=y_home, mappings=opened,
+            rows_home=max_rows, d=d, dtype=dtype, cap=cap, inbox=inbox, y_home=y_home, mappings=opened, sync=sync,
             inbox_ptrs=torch.tensor(in_ptrs, dtype=torch.int64, device=device),
             home_ptrs=torch.tensor(home_ptrs, dtype=torch.int64, device=device),
+            flag_ptrs=torch.tensor(sync_ptrs, dtype=torch.int64, device=device),
+            counts_ptrs=torch.tensor([p_ + 4 * counts_base for p_ in sync_ptrs], dtype=torch.int64, device=device),
+            counts_all=sync[counts_base:].view(2, w, self.e),
             yb=torch.empty((cap, d), dtype=dtype, device=device),
             targets=torch.zeros(cap, dtype=torch.int64, device=device),
             seg_base=torch.zeros(self.e, dtype=torch.int64, device=device),
             offsets=torch.zeros(self.el + 1, dtype=torch.int32, device=device),
-            flag=torch.zeros(1, dtype=torch.int32, device=device),
         )
         dist.barrier(group=self.group)
 
     def close(self):
-        """Unmap the peers' buffers (call before the process group goes away)."""
+        """Unmap the peers' buffers (collective in effect: call it on every rank, before the process
+        group goes away; no rank may still be inside a forward)."""
         if self._peer is not None:
             torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)  # nobody unmaps memory a peer's kernel may still store into
             for base in self._peer["mappings"].values():
                 check(lib.moe_ipc_close(base))
             self._peer = None
@@ -325,36 +347,72 @@ class EPMoELayer:
                                      torch.cuda.current_stream().cuda_stream))
         return pr["targets"]
 
-    def _rank_sync(self):
-        """Order the phases across ranks on the stream: a one-element all-reduce (no host wait)."""
-        dist.all_reduce(self._peer["flag"], group=self.group)
+    def _signal(self, slot: int, value: int, payload=None, payload_offset_words: int = 0):
+        """Tell every rank that this rank has reached phase `slot` of call `value` (its earlier stores,
+        the optional payload included, are visible to them before the flag is)."""
+        pr = self._peer
+        check(lib.moe_ep_signal(pr["flag_ptrs"].data_ptr(), self.world, self.rank, slot, value,
+                                payload.data_ptr() if payload is not None else None,
+                                pr["counts_ptrs"].data_ptr() if payload is not None else None,
+                                payload_offset_words, payload.numel() if payload is not None else 0,
+                                torch.cuda.current_stream().cuda_stream))
 
-    def forward_peer(self, x: torch.Tensor) -> torch.Tensor:
+    def _wait(self, slot: int, value: int):
+        """Stream-ordered wait (no host wait) until every rank has signalled phase `slot` of call
+        `value`; bounded on the device, a rank that never arrives shows up in ops.read_status()."""
+        pr = self._peer
+        ws = ops.workspace(pr["sync"].device, 1, self.e, self.k)
+        check(lib.moe_ep_wait(pr["sync"].data_ptr(), self.world, slot, value, ws.data_ptr(), ws.numel(),
+                              torch.cuda.current_stream().cuda_stream))
+
+    def _rank_sync(self, slot: int, value: int):
+        self._signal(slot, value)
+        self._wait(slot, value)
+
+    def exchange_counts_peer(self, counts, call: int):
+        """Every rank's per-expert counts into every rank's table (peer stores + a flag; replaces the
+        all-gather): returns the device tensor [W, E] of this call's parity."""
+        pr = self._peer
+        par = call & 1
+        self._signal(0, call, payload=counts, payload_offset_words=(par * self.world + self.rank) * self.e)
+        self._wait(0, call)
+        return pr["counts_all"][par]
+
+    def forward_peer(self, x: torch.Tensor, *, overlap: bool = True) -> torch.Tensor:
+        """overlap=True: the exchanges ride inside the kernels that produce the rows (the pack stores
+        into the owners' inboxes, the second expert GEMM stores its rows into their home slots).
+        overlap=False: every stage on its own, in series (local pack, push, FFN, push back)."""
         x = x.contiguous()
         rows_home, d = x.size(0) * self.k, x.size(1)
-        direct = self.direct_dispatch and (d * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
-        o = self.route_select(x) if direct else self.route(x)
-        if self._peer is None or self._peer["rows_home"] != rows_home or self._peer["d"] != d:
+        if self._peer is None:
             self._setup_peer(rows_home, d, x.dtype, x.device)
         pr = self._peer
-        counts_all = torch.empty((self.world, self.e), dtype=torch.int32, device=x.device)
-        dist.all_gather_into_tensor(counts_all, o["counts"], group=self.group)
-        # every rank has left the previous call's combine before anybody overwrites an inbox: the
-        # all-gather above is that barrier (it completes only when every rank has reached it)
+        if rows_home > pr["rows_home"] or d != pr["d"] or x.dtype != pr["dtype"]:
+            raise RuntimeError(f"EPMoELayer: batch of {x.size(0)} tokens x {d} does not fit the buffers set up for "
+                               f"{pr['rows_home'] // self.k} tokens x {pr['d']} per rank (pass max_tokens)")
+        self._calls += 1
+        call = self._calls
+        direct = overlap and self.direct_dispatch and (d * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
+        fuse = overlap and self.fuse_combine
+        o = self.route_select(x) if direct else self.route(x)
+        # Slot 0 doubles as the barrier that frees the buffers of the previous call: a rank signals it
+        # only after its own previous combine (stream order), and nobody stores into an inbox before
+        # every rank has signalled.
+        counts_all = self.exchange_counts_peer(o["counts"], call)
         if direct:
             self.dispatch_direct(x, o, counts_all)
         else:
             self._push(o["packed"], pr["inbox_ptrs"], counts_all, False, pr["offsets"])
-        if self.fuse_combine:
+        if fuse:
             targets = self._row_targets(counts_all)
-            self._rank_sync()  # all rows have arrived in every inbox
+            self._rank_sync(1, call)  # all rows have arrived in every inbox
             self._ffn(pr["inbox"], pr["offsets"], None, out_rows=targets)  # computes and returns the rows
         else:
-            self._rank_sync()
+            self._rank_sync(1, call)
             self._ffn(pr["inbox"], pr["offsets"], pr["yb"])
             self._push(pr["yb"], pr["home_ptrs"], counts_all, True, None)
-        self._rank_sync()  # all results are back in their home slots
-        out = ops.combine(pr["y_home"], o["gates"], o["route_row"], self.k)
+        self._rank_sync(2, call)  # all results are back in their home slots
+        out = ops.combine(pr["y_home"][:rows_home], o["gates"], o["route_row"], self.k)
         self.last = dict(counts_dev=counts_all, route=o)
         return out
 
@@ -362,7 +420,7 @@ class EPMoELayer:
         if not x.is_cuda:
             raise RuntimeError("inputs must be CUDA")
         if self.transport == "peer":
-            return self.forward_peer(x)
+            return self.forward_peer(x, overlap=overlap)
         main = torch.cuda.current_stream()
         comm = self.comm_stream if overlap else main
         if chunks is None:

@@ -22,7 +22,13 @@ from . import ops
 
 class HostRouter:
     def __init__(self, tokens: int, d_model: int, w_router: torch.Tensor, top_k: int = 2, *, depth: int = 2,
-                 skew_experts: int = 0, skew_bias: float = 0.0, device=None, upload_weight_each_call: bool = False):
+                 skew_experts: int = 0, skew_bias: float = 0.0, device=None, upload_weight_each_call: bool = False,
+                 download=None):
+        """`download`: names of the route outputs copied back to the host every call (default: all
+        seven: idx, gates, counts, offsets, packed, row_route, route_row).  A caller whose experts run
+        on the device leaves `packed` (k*T*d elements, almost all of the bytes) there and downloads
+        only the routing decision; the device tensors of the last call stay reachable through
+        `device_outputs(ticket)`."""
         if depth < 1:
             raise ValueError("depth must be >= 1")
         if w_router.dim() != 2 or w_router.size(1) != d_model:
@@ -40,7 +46,11 @@ class HostRouter:
             torch.cuda.synchronize(self.device)
             with torch.cuda.stream(s):
                 dev_out = ops.route_fused(x_dev, w_dev, self.k)  # allocates the outputs once
-            host_out = {n: torch.empty(v.shape, dtype=v.dtype).pin_memory() for n, v in dev_out.items() if n != "workspace"}
+            names = [n for n in dev_out if n != "workspace"] if download is None else list(download)
+            unknown = [n for n in names if n not in dev_out or n == "workspace"]
+            if unknown:
+                raise ValueError(f"unknown route outputs: {unknown}")
+            host_out = {n: torch.empty(dev_out[n].shape, dtype=dev_out[n].dtype).pin_memory() for n in names}
             self.slots.append(dict(stream=s, x=x_dev, w=w_dev, dev=dev_out, host=host_out,
                                    done=torch.cuda.Event(), busy=False))
         torch.cuda.synchronize(self.device)
@@ -80,6 +90,10 @@ class HostRouter:
         slot["done"].synchronize()
         slot["busy"] = False
         return slot["host"]
+
+    def device_outputs(self, ticket: int) -> dict:
+        """The device-side outputs of a ticket's slot (valid until ticket + depth is submitted)."""
+        return self.slots[ticket % len(self.slots)]["dev"]
 
     def route(self, x_host: torch.Tensor) -> dict:
         return self.result(self.submit(x_host))

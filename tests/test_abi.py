@@ -69,6 +69,19 @@ def test_argument_errors_do_not_launch(lib):
     assert rc == 1 and "16 bytes" in lib.last_error()
     assert L.moe_grouped_gemm(None, None, None, None, 4, 0, 64, 64, lib.MOE_W_NK, 0, lib.MOE_ACT_NONE, None, None,
                               lib.MOE_F16, 0, None, 0, None) == 0  # zero rows: nothing to do
+    # host-visible pointers that the kernels access 128 bits at a time must be 16-byte aligned
+    rc = L.moe_grouped_gemm(ctypes.c_void_p(4096), ctypes.c_void_p(4096), ctypes.c_void_p(4096 + 8), ctypes.c_void_p(4096),
+                            4, 16, 64, 64, lib.MOE_W_NK, 0, lib.MOE_ACT_NONE, None, None, lib.MOE_F16, 0,
+                            ctypes.c_void_p(4096), 1 << 20, None)
+    assert rc == 1 and "aligned" in lib.last_error()
+    rc = L.moe_ep_push(ctypes.c_void_p(4096 + 2), ctypes.c_void_p(4096), ctypes.c_void_p(4096), 8, 4, 0, 0, 64, 2, None, None)
+    assert rc == 1 and "aligned" in lib.last_error()
+    rc = L.moe_ep_signal(None, 4, 0, 0, 1, None, None, 0, 0, None)
+    assert rc == 1 and "flag table" in lib.last_error()
+    rc = L.moe_ep_wait(None, 4, 0, 1, None, 0, None)
+    assert rc == 1
+    assert L.moe_set_wait_limit(None, 0, 1000, None) == 3
+    assert L.moe_launch_count() >= 0 and L.moe_set_pdl(1) == 0
     # zero tokens is a valid no-op that needs no pointers
     assert L.moe_topk_select(None, lib.MOE_F16, 0, 64, 2, None, None, None) == 0
     assert L.moe_combine(None, lib.MOE_F16, None, None, 0, 8, 2, None, None) == 0

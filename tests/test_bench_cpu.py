@@ -8,15 +8,33 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_reference_arm_prints_the_contract_line():
-    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
-                          "--warmup", "1"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2",
+                          "--warmup", "3"], capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["higher_is_better"] is True
     assert line["value"] > 1e3 and line["ms_per_step"] > 0
-    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    # the reference's own bench_router.py when it has been staged under oracle/_ref, else the port
+    from oracle import ref_runner
+
+    assert line["cpu_baseline"]["kind"] == ("reference" if ref_runner.available() else "port")
+    assert line["cpu_baseline"]["cores"] >= 1 and line["steps"] == 2 and line["warmup"] == 3
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["gpu_launches"] == 0
-    assert "T=4096" in line["config"]["workload"]
+    # same workload string as the GPU arm prints, so that the two lines compare like for like
+    sys.path.insert(0, ROOT)
+    import bench
+
+    assert line["config"] == {"workload": bench.WORKLOAD}
+
+
+def test_reference_runner_falls_back_to_the_port_when_nothing_is_staged(monkeypatch):
+    sys.path.insert(0, ROOT)
+    import bench
+    from oracle import ref_runner
+
+    monkeypatch.setattr(ref_runner, "available", lambda: False)
+    r = bench.run_cpu_reference(1, 1)
+    assert r["kind"] == "port" and r["value"] > 1e3 and set(r["breakdown_ms"]) == {"t_logit", "t_select", "t_pack"}
 
 
 def test_non_zero_ranks_of_the_reference_arm_stay_silent():

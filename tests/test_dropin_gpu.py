@@ -182,8 +182,11 @@ def test_moe_layer_matches_reference_golden(pkg, golden_dir):
             ex.w3.weight.copy_(torch.from_numpy(g["w3"][i]))
             ex.w2.weight.copy_(torch.from_numpy(g["w2"][i]))
     x = torch.from_numpy(g["x"]).half().cuda()
-    y = layer(x)
-    assert tuple(y.shape) == tuple(g["y"].shape)
+    with pytest.raises(RuntimeError, match="forward-only"):  # gradients are on and the weights require them
+        layer(x)
+    with torch.no_grad():
+        y = layer(x)
+    assert tuple(y.shape) == tuple(g["y"].shape) and not y.requires_grad
     # rows whose routing is the same in fp16 as in the fp32 reference
     logits16 = oracle.router_logits(x.view(-1, d).cpu().numpy(), layer.router.weight.detach().cpu().numpy())
     idx16, _, _ = oracle.topk_select(logits16, k)
@@ -203,13 +206,14 @@ def test_moe_layer_matches_oracle(pkg, e, router):
     torch.manual_seed(3)
     d, h, k = 256, 512, 2
     impl = SinkhornRouter(iters=5) if router == "sinkhorn" else None
-    layer = MoELayer(d, h, e, k, router_impl=impl, track_metrics=True).half().cuda()
+    layer = MoELayer(d, h, e, k, router_impl=impl, track_metrics=True).half().cuda().requires_grad_(False)
     x = torch.randn(4, 100, d, device="cuda").half()
     y = layer(x)
     flat = x.view(-1, d)
     # routing actually used by the layer, recomputed through the same kernels
-    if router == "sinkhorn" or e == 8:
-        idx, w = layer.router_impl(layer.router(flat), k)
+    _i, _g, logits32 = pkg.ops.router_gemm_select(flat, layer.router.weight, k, return_logits=True)
+    if router == "sinkhorn":
+        idx, w = layer.router_impl(logits32.half(), k)
         gates = w.float()
     else:
         o = pkg.ops.route_fused(flat, layer.router.weight, k)
@@ -221,8 +225,61 @@ def test_moe_layer_matches_oracle(pkg, e, router):
     got = y.float().cpu().numpy().reshape(-1, d)
     scale = np.abs(ref.astype(np.float32)).max()
     np.testing.assert_allclose(got, ref.astype(np.float32), rtol=2e-2, atol=2e-2 * scale)
+    # the metrics record of models/decoder_moe.py:283-348, against the same formulas in numpy
+    from moe_routers_b200.metrics import MoEMetrics
+
     m = layer.get_last_metrics()
-    assert m["tokens"] == 400 and int(m["route_counts"].sum()) == 400 * k
+    assert isinstance(m, MoEMetrics) and m.router_backend == layer.router_impl.name
+    s_tok = 400
+    idx_np = idx.cpu().numpy().astype(np.int64)
+    counts = np.bincount(idx_np.reshape(-1), minlength=e).astype(np.float64)
+    p_route = counts / (s_tok * k)
+    nz = p_route[p_route > 0]
+    ent = float(-(nz * np.log(nz)).sum())
+    lg = logits32.float().cpu().numpy().astype(np.float64)
+    probs = np.exp(lg - lg.max(axis=1, keepdims=True))
+    probs /= probs.sum(axis=1, keepdims=True)
+    assert m.performance.tokens == s_tok
+    assert m.performance.total_moe_ms > 0 and m.performance.router_ms > 0 and m.performance.expert_ms > 0
+    assert abs(m.performance.token_latency_us - m.performance.total_moe_ms * 1000.0 / s_tok) < 1e-6
+    np.testing.assert_allclose(m.routing.route_distribution.numpy(), p_route, atol=1e-6)
+    assert abs(m.routing.routing_entropy - ent) < 1e-4
+    assert abs(m.routing.normalized_entropy - ent / np.log(e)) < 1e-4
+    assert abs(m.routing.mean_topk_probability - np.sort(probs, axis=1)[:, -k:].sum(axis=1).mean()) < 2e-3
+    assert abs(m.routing.top1_route_fraction - p_route.max()) < 1e-6
+    np.testing.assert_allclose(m.routing.per_token_prob_sample.numpy(), probs[0], atol=2e-3)
+    mean, std = counts.mean(), counts.std()
+    assert m.usage.active_experts == int((counts > 0).sum()) and m.usage.dead_experts == e - m.usage.active_experts
+    assert abs(m.usage.load_mean_routes - mean) < 1e-3 and abs(m.usage.load_std_routes - std) < 1e-2
+    assert abs(m.usage.load_cv - std / (mean + 1e-9)) < 1e-4
+    assert abs(m.usage.load_max_over_mean - counts.max() / (mean + 1e-9)) < 1e-4
+    assert abs(m.usage.load_min_over_mean - counts.min() / (mean + 1e-9)) < 1e-4
+    assert abs(m.usage.avg_active_experts_per_token - k) < 1e-6  # top-k picks are distinct
+    assert abs(m.usage.aux_load_balance_loss - e * float((p_route * probs.mean(axis=0)).sum())) < 2e-3
+    uniq = np.array([len(set(np.nonzero((idx_np == ex).any(axis=1))[0])) for ex in range(e)], dtype=np.float64)
+    assert abs(m.usage.unique_tokens_per_expert_mean - uniq.mean()) < 1e-3
+    assert abs(m.usage.unique_tokens_per_expert_std - uniq.std()) < 1e-2
+    assert abs(m.output["abs_max"] - np.abs(got).max()) < 1e-3
+
+
+def test_decoder_moe_block_wraps_the_dropin_layer(pkg):
+    """The reference-shaped block (models/decoder_moe.py:353-391): x + attn(attn_norm(x)), then
+    x + moe(moe_norm(x)), with caller-supplied attention and norms around the drop-in MoE layer."""
+    from moe_routers_b200.moe_layer import DecoderMoEBlock, MoELayer
+
+    torch.manual_seed(5)
+    d, h, e, k = 128, 256, 8, 2
+    attn = torch.nn.Linear(d, d, bias=False)
+    blk = DecoderMoEBlock(d, h, e, k, attn=attn, attn_norm=torch.nn.LayerNorm(d), moe_norm=torch.nn.LayerNorm(d),
+                          track_metrics=True).half().cuda()
+    assert isinstance(blk.moe, MoELayer) and blk.moe.top_k == k and len(blk.moe.experts) == e
+    x = torch.randn(2, 40, d, device="cuda").half()
+    with torch.no_grad():
+        y = blk(x)
+        x1 = x + blk.attn(blk.attn_norm(x))
+        ref = x1 + blk.moe(blk.moe_norm(x1))
+    assert torch.equal(y, ref)  # the kernels are deterministic
+    assert blk.moe.get_last_metrics().performance.tokens == 80
 
 
 @pytest.mark.parametrize("strategy", ["naive_topk", "fused_select", "sinkhorn", "masked_matmul"])

@@ -244,6 +244,75 @@ def test_scatter_to_and_gemm_rows_edge_cases():
                      out_rows=torch.zeros(1, dtype=torch.int64, device="cuda"))
 
 
+def test_rank_signals_emulated_ranks():
+    """moe_ep_signal / moe_ep_wait with all ranks emulated on one GPU.  Kernels that wait on one
+    another must not share a GPU, so every rank signals first and only then do the ranks wait: each
+    wait finds its flags already set.  Checks the payload (per-expert counts) in every rank's table,
+    two calls in a row (values grow, nothing is cleared) and a clean status."""
+    _need_cuda()
+    from moe_routers_b200 import _lib, ops
+
+    world, e = 4, 16
+    tables = [torch.zeros(3 * world + 2 * world * e, dtype=torch.int32, device="cuda") for _ in range(world)]
+    flag_ptrs = torch.tensor([t.data_ptr() for t in tables], dtype=torch.int64, device="cuda")
+    counts_ptrs = torch.tensor([t.data_ptr() + 4 * 3 * world for t in tables], dtype=torch.int64, device="cuda")
+    ws = ops.workspace(torch.device("cuda", torch.cuda.current_device()), 1, e, 2)
+    st = torch.cuda.current_stream().cuda_stream
+    rng = np.random.default_rng(0)
+    for call in (1, 2):
+        par = call & 1
+        counts = [torch.from_numpy(rng.integers(0, 99, size=e).astype(np.int32)).cuda() for _ in range(world)]
+        for r in range(world):
+            _lib.check(_lib.lib.moe_ep_signal(flag_ptrs.data_ptr(), world, r, 0, call, counts[r].data_ptr(),
+                                              counts_ptrs.data_ptr(), (par * world + r) * e, e, st))
+            _lib.check(_lib.lib.moe_ep_signal(flag_ptrs.data_ptr(), world, r, 2, call, None, None, 0, 0, st))
+        for r in range(world):
+            _lib.check(_lib.lib.moe_ep_wait(tables[r].data_ptr(), world, 0, call, ws.data_ptr(), ws.numel(), st))
+            _lib.check(_lib.lib.moe_ep_wait(tables[r].data_ptr(), world, 2, call, ws.data_ptr(), ws.numel(), st))
+        torch.cuda.synchronize()
+        for r in range(world):
+            tab = tables[r].cpu().numpy()
+            np.testing.assert_array_equal(tab[0:world], call)                 # slot 0
+            np.testing.assert_array_equal(tab[world:2 * world], 0)            # slot 1 untouched
+            np.testing.assert_array_equal(tab[2 * world:3 * world], call)     # slot 2
+            got = tab[3 * world:].reshape(2, world, e)[par]
+            np.testing.assert_array_equal(got, np.stack([c.cpu().numpy() for c in counts]))
+    assert ops.read_status() == 0
+
+
+def test_wait_that_runs_out_reports_instead_of_hanging():
+    """Failure detection without a GPU fault: a wait for a rank that never signals runs out after the
+    workspace's wait limit (set to 2 ms here), the kernel returns, the status block names the rank,
+    moe_read_status maps it to MOE_ERR_DEVICE, and the context stays usable."""
+    _need_cuda()
+    import ctypes
+    import time
+
+    from moe_routers_b200 import _lib
+
+    world = 4
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    table = torch.zeros(3 * world, dtype=torch.int32, device="cuda")
+    table[0:world] = torch.tensor([1, 1, 0, 1], dtype=torch.int32)  # rank 2 never arrived at call 1
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib.moe_workspace_init(ws.data_ptr(), ws.numel(), st))
+    _lib.check(_lib.lib.moe_set_wait_limit(ws.data_ptr(), ws.numel(), 2_000_000, st))
+    t0 = time.time()
+    _lib.check(_lib.lib.moe_ep_wait(table.data_ptr(), world, 0, 1, ws.data_ptr(), ws.numel(), st))
+    out = ctypes.c_int(0)
+    rc = _lib.lib.moe_read_status(ws.data_ptr(), st, ctypes.byref(out))
+    assert time.time() - t0 < 5.0
+    assert rc == _lib.MOE_ERR_DEVICE and out.value == (0x400 | 2)
+    assert "peer rank" in _lib.last_error()
+    with pytest.raises(_lib.MoeError):
+        _lib.check(rc)
+    # the context is alive: clear the status block and run a wait that is satisfied
+    _lib.check(_lib.lib.moe_workspace_init(ws.data_ptr(), ws.numel(), st))
+    table[2] = 1
+    _lib.check(_lib.lib.moe_ep_wait(table.data_ptr(), world, 0, 1, ws.data_ptr(), ws.numel(), st))
+    assert _lib.lib.moe_read_status(ws.data_ptr(), st, ctypes.byref(out)) == 0 and out.value == 0
+
+
 def _ep_worker(rank, world, port, strategy, q):
     try:
         import torch.distributed as dist
@@ -272,15 +341,17 @@ def _ep_worker(rank, world, port, strategy, q):
                                  strategy=strategy, skew_experts=4, skew_bias=2.0, transport=tr)
                   for tr in ("peer", "nccl")}
         outs = {}
+        # peer: fused exchanges twice in a row (buffers and flags are reused), the unfused kernels under
+        # overlap=True, and the serial chain (overlap=False); nccl: two streams and one stream
         for tr, overlap, fuse in (("peer", True, True), ("peer", True, True), ("peer", True, False),
-                                  ("nccl", True, None), ("nccl", False, None)):
+                                  ("peer", False, True), ("nccl", True, None), ("nccl", False, None)):
             layer = layers[tr]
             if fuse is not None:
                 layer.fuse_combine = fuse  # second GEMM returns its rows itself / dense result + push
                 layer.direct_dispatch = fuse  # pack stores into the owners' inboxes / local pack + push
             out = layer(x.cuda(), overlap=overlap)
             torch.cuda.synchronize()
-            outs[(tr, fuse)] = out.clone()
+            outs[(tr, fuse, overlap)] = out.clone()
             o = layer.last["route"]
             experts = {"w1": w1.float().numpy(), "w2": w2.float().numpy()}
             ref, _ = oracle.moe_layer(x.float().numpy(), o["idx"].cpu().numpy(), o["gates"].cpu().numpy(), experts,
@@ -290,7 +361,18 @@ def _ep_worker(rank, world, port, strategy, q):
             # layer outputs: 2e-2 relative to the output scale (fp16), 6e-2 for bf16
             np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=tol, atol=tol * scale)
         # the same kernels did the arithmetic in both peer variants: identical bits
-        assert torch.equal(outs[("peer", True)], outs[("peer", False)])
+        assert torch.equal(outs[("peer", True, True)], outs[("peer", False, True)])
+        assert torch.equal(outs[("peer", True, True)], outs[("peer", True, False)])
+        from moe_routers_b200 import ops as _ops
+
+        assert _ops.read_status() == 0  # no bounded wait (mbarrier, rank signal) gave up
+        # a batch larger than the buffers set up at the first call is refused, on every rank alike
+        big = torch.zeros((t + 2048, d), dtype=dt, device="cuda")
+        try:
+            layers["peer"](big)
+            raise AssertionError("oversized batch was accepted")
+        except RuntimeError as exc:
+            assert "max_tokens" in str(exc)
         dist.barrier()
         for layer in layers.values():
             layer.close()
