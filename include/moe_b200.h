@@ -342,6 +342,12 @@ int moe_ep_signal(void* const* peer_flags, int world, int rank, int slot, int va
                   void* const* peer_payload, size_t payload_offset_words, int payload_words, void* stream);
 int moe_ep_wait(const int32_t* flags, int world, int slot, int value, void* workspace, size_t workspace_bytes,
                 void* stream);
+/* moe_ep_signal followed by moe_ep_wait on the same slot and value, as ONE kernel launch (what the
+ * layer uses between its phases).  Only where every rank runs on its own GPU: with several ranks
+ * emulated on one GPU the wait would be for signals of launches queued behind it. */
+int moe_ep_sync(void* const* peer_flags, const int32_t* flags, int world, int rank, int slot, int value,
+                const int32_t* payload, void* const* peer_payload, size_t payload_offset_words, int payload_words,
+                void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Dispatch destinations: seg_base[g] (g = global expert) = address, inside inbox_bufs[owner of g]

@@ -46,6 +46,7 @@ SIGNATURES = {
     "moe_ep_push": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]),
     "moe_ep_signal": (_i, [_p, _i, _i, _i, _i, _p, _p, _sz, _i, _p]),
     "moe_ep_wait": (_i, [_p, _i, _i, _i, _p, _sz, _p]),
+    "moe_ep_sync": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _sz, _i, _p, _sz, _p]),
     "moe_sinkhorn": (_i, [_p, _i, _i, _i, _i, _i, _f, _f, _p, _p, _p, _sz, _p]),
     "moe_grouped_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),
     "moe_grouped_gemm_rows": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_int64, _i, _p, _p, _i, _i, _p, _sz, _p]),

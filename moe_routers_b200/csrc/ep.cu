@@ -378,6 +378,61 @@ ep_wait_kernel(const int32_t* __restrict__ flags, int world, int slot, int32_t v
 }  // namespace
 }  // namespace moe
 
+namespace moe {
+namespace {
+// signal + wait in one launch (one CTA): the layer's phase boundary costs one kernel, not two
+__global__ void __launch_bounds__(kThreads)
+ep_sync_kernel(int32_t* const* __restrict__ peer_flags, const int32_t* __restrict__ flags, int world, int rank, int slot,
+               int32_t value, const int32_t* __restrict__ payload, int32_t* const* __restrict__ peer_payload,
+               size_t payload_offset_words, int payload_words, int32_t* status) {
+  if (payload != nullptr) {
+    for (int i = threadIdx.x; i < payload_words * world; i += kThreads) {
+      const int p = i / payload_words, j = i - p * payload_words;
+      peer_payload[p][payload_offset_words + j] = payload[j];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  const int32_t* mine = flags + (size_t)slot * world;
+  for (int p = threadIdx.x; p < world; p += kThreads) {
+    st_release_sys(peer_flags[p] + (size_t)slot * world + rank, value);
+    bool seen = false;
+#pragma unroll 1
+    for (int i = 0; i < 4096 && !seen; ++i) seen = ld_acquire_sys(mine + p) - value >= 0;
+    if (!seen) {
+      const unsigned long long t0 = sm100::globaltimer_ns();
+      const unsigned long long limit = sm100::wait_limit_ns(status);
+      while (!seen) {
+#pragma unroll 1
+        for (int i = 0; i < 256 && !seen; ++i) seen = ld_acquire_sys(mine + p) - value >= 0;
+        if (!seen && sm100::globaltimer_ns() - t0 > limit) {
+          record_error(status, kErrPeerWait | (p & 0xff));
+          break;
+        }
+      }
+    }
+  }
+  __threadfence_system();
+}
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_ep_sync(void* const* peer_flags, const int32_t* flags, int world, int rank, int slot, int value,
+                           const int32_t* payload, void* const* peer_payload, size_t payload_offset_words,
+                           int payload_words, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace moe;
+  if (world <= 0 || world > kThreads || rank < 0 || rank >= world || slot < 0)
+    return fail(MOE_ERR_ARG, "moe_ep_sync: bad world / rank / slot");
+  if (!peer_flags || !flags) return fail(MOE_ERR_ARG, "moe_ep_sync: null flag table");
+  if (payload != nullptr && (!peer_payload || payload_words <= 0)) return fail(MOE_ERR_ARG, "moe_ep_sync: bad payload");
+  if (!workspace || workspace_bytes < (size_t)kStatusBytes) return fail(MOE_ERR_WORKSPACE, "moe_ep_sync: workspace missing");
+  ep_sync_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<int32_t* const*>(peer_flags), flags, world, rank, slot, value, payload,
+      reinterpret_cast<int32_t* const*>(peer_payload), payload_offset_words, payload ? payload_words : 0,
+      static_cast<int32_t*>(workspace));
+  return check_launch("ep_sync_kernel");
+}
+
 extern "C" int moe_ep_signal(void* const* peer_flags, int world, int rank, int slot, int value, const int32_t* payload,
                              void* const* peer_payload, size_t payload_offset_words, int payload_words, void* stream) {
   using namespace moe;

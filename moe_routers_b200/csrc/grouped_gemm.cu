@@ -297,6 +297,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    // (one issuing lane: with 48-64 KB of L2-resident operands per stage in two or three large boxes,
+    // several issuing lanes measured 0-5 % slower on every shape)
     if (lane == 0) {
       uint32_t it = 0;  // k-block counter across tiles
       bool ok = true;

@@ -143,18 +143,7 @@ __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// 32 lanes x 32 consecutive fp32 columns without the trailing wait (several loads in flight).
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
+// 32 lanes x 16 consecutive fp32 columns without the trailing wait (several loads in flight).
 __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -405,23 +394,33 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const uint32_t owner_part = map_to_cta(smem_u32(s_partial), (uint32_t)dest) + (uint32_t)((slot * S + krank) * 32 * EP) * 4u;
     for (int c0 = 0; c0 < E; c0 += kChunk) {
       const int width = min(kChunk, E - c0);  // 16, 32, 48 or 64 columns
-      // (1) sum the accumulators of this chunk: thread = row, registers = columns
+      // (1) sum the accumulators of this chunk: thread = row, registers = columns; all loads of the
+      // chunk are in flight together
       float v[kChunk];
+      {
+        uint32_t r[kMmaWarps][kChunk];
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i) v[i] = 0.f;
-      if (ok) {
-        for (int a = 0; a < p.nacc; ++a) {
-          if (!((mask >> a) & 1u)) continue;
+        for (int a = 0; a < kMmaWarps; ++a)
 #pragma unroll
-          for (int g = 0; g < kChunk / 16; ++g) {
-            if (g * 16 < width) {
-              uint32_t r16[16];
-              tmem_ld16_nowait(taddr + (uint32_t)(a * E + c0 + g * 16), r16);
-              tmem_ld_wait();
+          for (int i = 0; i < kChunk; ++i) r[a][i] = 0u;
+        if (ok) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) v[g * 16 + i] += __uint_as_float(r16[i]);
+          for (int a = 0; a < kMmaWarps; ++a) {
+            if (a < p.nacc && ((mask >> a) & 1u)) {
+#pragma unroll
+              for (int g = 0; g < kChunk / 16; ++g)
+                if (g * 16 < width)
+                  tmem_ld16_nowait(taddr + (uint32_t)(a * E + c0 + g * 16), reinterpret_cast<uint32_t(&)[16]>(r[a][g * 16]));
             }
           }
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) {
+          float acc = __uint_as_float(r[0][i]);
+#pragma unroll
+          for (int a = 1; a < kMmaWarps; ++a) acc += __uint_as_float(r[a][i]);
+          v[i] = acc;
         }
       }
       // (2) transpose through this warp's staging tile so that a store instruction covers whole rows

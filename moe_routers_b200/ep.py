@@ -347,35 +347,25 @@ class EPMoELayer:
                                      torch.cuda.current_stream().cuda_stream))
         return pr["targets"]
 
-    def _signal(self, slot: int, value: int, payload=None, payload_offset_words: int = 0):
-        """Tell every rank that this rank has reached phase `slot` of call `value` (its earlier stores,
-        the optional payload included, are visible to them before the flag is)."""
-        pr = self._peer
-        check(lib.moe_ep_signal(pr["flag_ptrs"].data_ptr(), self.world, self.rank, slot, value,
-                                payload.data_ptr() if payload is not None else None,
-                                pr["counts_ptrs"].data_ptr() if payload is not None else None,
-                                payload_offset_words, payload.numel() if payload is not None else 0,
-                                torch.cuda.current_stream().cuda_stream))
-
-    def _wait(self, slot: int, value: int):
-        """Stream-ordered wait (no host wait) until every rank has signalled phase `slot` of call
-        `value`; bounded on the device, a rank that never arrives shows up in ops.read_status()."""
+    def _rank_sync(self, slot: int, value: int, payload=None, payload_offset_words: int = 0):
+        """Tell every rank that this rank has reached phase `slot` of call `value` (its earlier stores, the
+        optional payload included, are visible to them before the flag is) and wait, on the stream, until
+        every rank has done the same: one launch, no host wait.  The wait is bounded on the device; a
+        rank that never arrives shows up in ops.read_status()."""
         pr = self._peer
         ws = ops.workspace(pr["sync"].device, 1, self.e, self.k)
-        check(lib.moe_ep_wait(pr["sync"].data_ptr(), self.world, slot, value, ws.data_ptr(), ws.numel(),
-                              torch.cuda.current_stream().cuda_stream))
-
-    def _rank_sync(self, slot: int, value: int):
-        self._signal(slot, value)
-        self._wait(slot, value)
+        check(lib.moe_ep_sync(pr["flag_ptrs"].data_ptr(), pr["sync"].data_ptr(), self.world, self.rank, slot, value,
+                              payload.data_ptr() if payload is not None else None,
+                              pr["counts_ptrs"].data_ptr() if payload is not None else None,
+                              payload_offset_words, payload.numel() if payload is not None else 0,
+                              ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
 
     def exchange_counts_peer(self, counts, call: int):
         """Every rank's per-expert counts into every rank's table (peer stores + a flag; replaces the
         all-gather): returns the device tensor [W, E] of this call's parity."""
         pr = self._peer
         par = call & 1
-        self._signal(0, call, payload=counts, payload_offset_words=(par * self.world + self.rank) * self.e)
-        self._wait(0, call)
+        self._rank_sync(0, call, payload=counts, payload_offset_words=(par * self.world + self.rank) * self.e)
         return pr["counts_all"][par]
 
     def forward_peer(self, x: torch.Tensor, *, overlap: bool = True) -> torch.Tensor:
