@@ -18,7 +18,8 @@
  *     path: MOE_B200_PDL=0 (no programmatic dependent launch between the
  *     route kernels; moe_set_pdl changes it at run time), MOE_B200_M64=0
  *     and MOE_B200_PAIR=0 (grouped GEMM: 128-row tiles only / single-tile
- *     work units), MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
+ *     work units), MOE_B200_GEMM_PRODUCERS=1 (grouped GEMM: one TMA-issuing
+ *     warp), MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
  *
  * Each declaration names the piece of the reference (path:lines inside
  * santiweide/moe-routers) that it replaces.

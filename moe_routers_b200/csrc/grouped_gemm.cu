@@ -45,7 +45,9 @@ using namespace sm100;
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kUK = 16;
-constexpr int kThreads = 320;  // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
+constexpr int kThreads = 352;  // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue, warp 10 second producer
+constexpr int kEpiThreads = 256;
+constexpr int kProducerWarps = 2;
 constexpr int kABytes = kBM * kBK * 2;
 constexpr int kMaxStages = 8;
 constexpr int kMaxExperts = 1024;
@@ -63,6 +65,7 @@ struct GParams {
   int pair_min_avg;         // pair mode when the experts hold at least this many rows on average (0: never)
   int stages_pair;          // pipeline depth in pair mode (stages: single-tile units)
   int stage_area;           // bytes reserved for the stage ring (the larger of the two layouts)
+  int producers;            // warps that issue TMA copies with single-tile units (1..2)
   int m64;                  // 1: a last tile of <= 64 rows runs as UMMA M=64; 0: every tile is 128 rows
   int32_t* status;
 };
@@ -252,7 +255,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, kThreads - 64);  // every epilogue thread arrives
+      mbar_init(tempty0 + 8 * b, kEpiThreads);  // every epilogue thread arrives
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -295,11 +298,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int total_tiles = (s_mt[p.experts] + s_mb[p.experts]) * p.n_tiles;
   const bool swiglu = p.act == MOE_ACT_SWIGLU;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    // (one issuing lane: with 48-64 KB of L2-resident operands per stage in two or three large boxes,
-    // several issuing lanes measured 0-5 % slower on every shape)
-    if (lane == 0) {
+  if (warp == 0 || warp >= 10) {
+    // ------------------------------ TMA producers ------------------------------
+    // The bulk tensor copies of ONE thread are served one after another (about 0.35 us each on B200).
+    // With single-tile units (two boxes per 48 KiB stage, four stages) a second issuing warp measured
+    // 5-6 % faster (32 x 256 rows: 1228 -> 1163 us, 64 x 128: 1539 -> 1454 us); pair-mode units are not
+    // issue-bound and measured 0-3 % slower with it, so they keep one.  Producer j owns the stages s
+    // with s % producers == j and fills them in order (a stage's barrier parity is never ambiguous).
+    // MOE_B200_GEMM_PRODUCERS=1 in the environment keeps one issuing warp everywhere.
+    const int pw = warp == 0 ? 0 : warp - 9;
+    const int producers = pair ? 1 : min(p.producers, n_stages);
+    if (lane == 0 && pw < producers) {
       uint32_t it = 0;  // k-block counter across tiles
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -308,6 +317,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const bool two = u.two;  // the unit has a second tile
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = (int)(it % (uint32_t)n_stages);
+          if (s % producers != pw) continue;
           const uint32_t ph = (it / (uint32_t)n_stages) & 1u;
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1)) { ok = false; break; }
           mbar_expect_tx(full0 + 8 * s, (uint32_t)(kABytes * (two ? 2 : 1) + b_bytes));
@@ -502,6 +512,14 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
     // last tile as UMMA M=64 when it holds at most 64 rows: half the tensor time for that tile)
     static const int m64 = [] { const char* v = getenv("MOE_B200_M64"); return (v && v[0] == '0') ? 0 : 1; }();
     p.m64 = m64;
+  }
+  {
+    static const int producers = [] {
+      const char* v = getenv("MOE_B200_GEMM_PRODUCERS");
+      const int n = v ? atoi(v) : kProducerWarps;
+      return n < 1 ? 1 : (n > kProducerWarps ? kProducerWarps : n);
+    }();
+    p.producers = producers;
   }
   p.bias = static_cast<const uint16_t*>(bias);
   p.bf16 = dtype == MOE_BF16;
