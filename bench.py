@@ -15,7 +15,7 @@ Prints ONE JSON line (rank 0).  Keys beyond the common contract:
   roofline      the whole step: 101,253,636 algorithmic bytes / ms_per_step against the measured
                 HBM copy peak; `kernels` holds each kernel timed alone back to back, and the step
                 with the overlap between the two kernels switched off
-  peaks_local   copy / read-only / write-only / 1 read : 2 write streams measured in this run
+  peaks_local   copy / read-only / write-only streams measured in this run
   select_pack_roofline   the reference's own operator (logits given): select + count + scan + pack
   strategies    the other routing strategies and the expert FFN shapes of the benchmark
                 configurations (single GPU), each with its own roofline figure
@@ -50,8 +50,8 @@ ROUTER_BYTES = T * D * 2 + E * D * 2 + 2 * T * K_TOP * 4 + (T // 32) * E * 4  # 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (router kernel: exactly its reads; scatter: the L2 still holds most of the 67 MB written
 # when the kernel ends, hence less than the algorithmic bytes)
-ROUTER_DRAM_TRAFFIC = 34_130_000
-SCATTER_DRAM_TRAFFIC = 42_600_000
+ROUTER_DRAM_TRAFFIC = 34_150_000
+SCATTER_DRAM_TRAFFIC = 42_900_000
 WORKLOAD = "fused_select T=4096 d_model=4096 E=64 top_k=2 fp16, +2.0 skew on experts 0..7"
 METRIC = "routed tokens/s per MoE layer"
 
@@ -389,7 +389,6 @@ def main_ours(args):
             "copy": 2 * nb / event_us(lambda: b_buf[:n_el].copy_(a_buf)) / 1e3,
             "read_only": nb / event_us(lambda: a_buf.sum()) / 1e3,
             "write_only": 2 * nb / event_us(lambda: b_buf.zero_()) / 1e3,
-            "read1_write2": 3 * nb / event_us(lambda: b_buf.view(2, n_el).copy_(a_buf.expand(2, n_el))) / 1e3,
         }
         del a_buf, b_buf
         torch.cuda.empty_cache()
@@ -568,9 +567,11 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
                                   "reference_traffic_model_bytes": (2 + 4 * 10) * 2 * T * E * 4}
     # combine
     o = ops.route_fused(xs[0], w, K_TOP)
-    us = graph_us(lambda i: ops.combine(o["packed"], o["gates"], o["route_row"], K_TOP))
+    ys = [o["packed"]] + [o["packed"].clone() for _ in range(3)]  # 4 x 67 MB of expert outputs > L2
+    us = graph_us(lambda i: ops.combine(ys[i % len(ys)], o["gates"], o["route_row"], K_TOP))
     out["combine"] = {"t_us": us, "bound": "hbm", "algorithmic_bytes": PACK_BYTES,
-                      "frac": PACK_BYTES / (us * 1e-6) / 1e9 / peak}
+                      "frac": PACK_BYTES / (us * 1e-6) / 1e9 / peak, "inputs": "4 rotating expert-output buffers"}
+    del ys
     # grouped expert FFN 4096 -> 8192 -> 4096 on 8192 routed rows: 8 experts x 1024 rows (tensor-bound),
     # 64 experts x 128 rows (weight-bound)
     flops = 2.0 * T * K_TOP * (D * HID + HID * D)

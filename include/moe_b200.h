@@ -318,6 +318,10 @@ int moe_enable_peer_access(int peer_device);
  * from the current device.  Setup helpers; the reference has no counterpart. */
 int moe_ipc_open(const void* handle64, void** base_out);
 int moe_ipc_close(void* base);
+/* Export side: the 64-byte IPC handle of the device allocation that contains `ptr` (host buffer
+ * handle64_out) and the byte offset of `ptr` inside that allocation; the peer maps the handle with
+ * moe_ipc_open and adds the offset.  The allocation must come from cudaMalloc. */
+int moe_ipc_export(const void* ptr, void* handle64_out, size_t* offset_out);
 
 int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts, int world,
                 int rank, int combine, int d, int elem_bytes, int32_t* local_offsets, void* stream);

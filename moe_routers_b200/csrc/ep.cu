@@ -494,6 +494,37 @@ extern "C" int moe_ipc_open(const void* handle64, void** base_out) {
   return MOE_OK;
 }
 
+// Export side of moe_ipc_open: the 64-byte IPC handle of the allocation that contains `ptr` and the
+// offset of `ptr` inside it (a tensor of a caching allocator usually sits inside a larger block).
+extern "C" int moe_ipc_export(const void* ptr, void* handle64_out, size_t* offset_out) {
+  using namespace moe;
+  if (!ptr || !handle64_out || !offset_out) return fail(MOE_ERR_ARG, "moe_ipc_export: null pointer");
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<RangeFn>(fn);
+  }();
+  if (!range) return fail(MOE_ERR_LAUNCH, "moe_ipc_export: cuMemGetAddressRange is not available from this driver");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS || base == 0)
+    return fail(MOE_ERR_ARG, "moe_ipc_export: not a device allocation");
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(MOE_ERR_UNSUPPORTED, "moe_ipc_export: %s (the buffer must come from cudaMalloc, not a virtual-memory pool)",
+                cudaGetErrorString(e));
+  }
+  memcpy(handle64_out, &h, sizeof(h));
+  *offset_out = reinterpret_cast<uintptr_t>(ptr) - static_cast<uintptr_t>(base);
+  return MOE_OK;
+}
+
 extern "C" int moe_ipc_close(void* base) {
   using namespace moe;
   if (!base) return MOE_OK;

@@ -272,16 +272,12 @@ class EPMoELayer:
         sync = torch.zeros(3 * w + 2 * w * self.e, dtype=torch.int32, device=device)
 
         def export(t):
-            # (device, ipc handle of the allocation's base, size, offset of the storage in it, ...)
-            meta = t.untyped_storage()._share_cuda_()
-            handle = bytes(meta[1])
-            if len(handle) == 66:  # torch prefixes a version byte and a kind byte ('c' = cudaMalloc)
-                if handle[1:2] != b"c":
-                    raise RuntimeError("peer transport needs cudaMalloc-backed tensors (no expandable segments)")
-                handle = handle[2:]
-            if len(handle) != 64:
-                raise RuntimeError(f"unexpected CUDA IPC handle size {len(handle)}")
-            return handle, int(meta[3]) + t.storage_offset() * t.element_size()
+            """(64-byte IPC handle of the allocation holding `t`, offset of `t` inside it)"""
+            handle = ctypes.create_string_buffer(64)
+            offset = ctypes.c_size_t(0)
+            with torch.cuda.device(device):
+                check(lib.moe_ipc_export(t.data_ptr(), handle, ctypes.byref(offset)))
+            return handle.raw, int(offset.value)
 
         gathered = [None] * w
         if w > 1:

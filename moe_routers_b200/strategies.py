@@ -49,13 +49,48 @@ def masked_matmul_forward(x: torch.Tensor, r: dict, w1: torch.Tensor, w2: torch.
     if e > 8:
         raise RuntimeError("masked_matmul_forward supports at most 8 experts")
     dev = x.device
-    seg = torch.tensor([0, t], dtype=torch.int32, device=dev)
+    seg = _one_segment(t, dev)
     y = torch.empty((e * t, d), dtype=x.dtype, device=dev)
     for ex in range(e):  # one dense GEMM pair per expert, no host synchronisation
         h = ops.grouped_gemm(x, w1[ex:ex + 1], seg, layout="nk", activation=activation)
         ops.grouped_gemm(h, w2[ex:ex + 1], seg, layout="nk", out=y[ex * t:(ex + 1) * t])
+    # the combine kernel sums E rows per token: dense gates [T, E] (zero for unselected experts) and the
+    # row of expert ex's result for token t, ex * T + t (a constant table, built once per shape)
     dense = torch.zeros((t, e), dtype=torch.float32, device=dev)
     dense.scatter_add_(1, r["idx"].long(), r["gates"])
-    rows = (torch.arange(e, device=dev, dtype=torch.int32).view(1, e) * t
-            + torch.arange(t, device=dev, dtype=torch.int32).view(t, 1)).contiguous()
-    return ops.combine(y, dense, rows.view(-1), e)
+    return ops.combine(y, dense, _dense_rows(t, e, dev), e)
+
+
+_dense_rows_cache: dict = {}
+
+
+def _dense_rows(t: int, e: int, dev) -> torch.Tensor:
+    """int32 [t * e]: entry t * e + ex = ex * t + t_index, built once per (t, e, device)."""
+    key = (t, e, dev)
+    rows = _dense_rows_cache.get(key)
+    if rows is None:
+        rows = (torch.arange(e, device=dev, dtype=torch.int32).view(1, e) * t
+                + torch.arange(t, device=dev, dtype=torch.int32).view(t, 1)).contiguous().view(-1)
+        _dense_rows_cache[key] = rows
+    return rows
+
+
+_segment_cache: dict = {}
+
+
+def _one_segment(t: int, dev) -> torch.Tensor:
+    """offsets [0, t] of a single expert segment on `dev`, uploaded once per (t, device)."""
+    key = (t, dev)
+    seg = _segment_cache.get(key)
+    if seg is None:
+        seg = _segment_cache[key] = torch.tensor([0, t], dtype=torch.int32, device=dev)
+    return seg
+
+
+def _token_ids(t: int, dev) -> torch.Tensor:
+    """int32 [t, 1] column 0..t-1 on `dev`, built once per (t, device)."""
+    key = (t, dev)
+    ids = _token_id_cache.get(key)
+    if ids is None:
+        ids = _token_id_cache[key] = torch.arange(t, device=dev, dtype=torch.int32).view(t, 1)
+    return ids

@@ -80,6 +80,7 @@ def test_argument_errors_do_not_launch(lib):
     assert rc == 1 and "flag table" in lib.last_error()
     rc = L.moe_ep_wait(None, 4, 0, 1, None, 0, None)
     assert rc == 1
+    assert L.moe_ipc_export(None, None, None) == 1 and "null" in lib.last_error()
     assert L.moe_set_wait_limit(None, 0, 1000, None) == 3
     assert L.moe_launch_count() >= 0 and L.moe_set_pdl(1) == 0
     # zero tokens is a valid no-op that needs no pointers

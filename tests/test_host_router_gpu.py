@@ -65,3 +65,30 @@ def test_host_router_rejects_misuse():
     r.result(tk)
     with pytest.raises(RuntimeError):
         r.result(tk)
+
+
+def test_host_router_download_subset():
+    """`download=` brings back only the routing decision; the packed rows stay on the device, where
+    `device_outputs` hands them to the expert GEMMs; the byte counts the benchmark declares follow."""
+    from moe_routers_b200.host import HostRouter
+
+    t, d, e, k = 256, 128, 16, 2
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(e, d, generator=g) / d ** 0.5).half()
+    x = torch.randn(t, d, generator=g).half().pin_memory()
+    names = ("idx", "gates", "counts", "offsets", "row_route", "route_row")
+    r = HostRouter(t, d, w, k, depth=2, download=names)
+    full = HostRouter(t, d, w, k, depth=1)
+    tk = r.submit(x)
+    o = r.result(tk)
+    ref = full.route(x)
+    assert sorted(o) == sorted(names)
+    for n in names:
+        assert torch.equal(o[n], ref[n]), n
+    dev = r.device_outputs(tk)
+    assert torch.equal(dev["packed"].cpu(), ref["packed"])
+    assert r.d2h_bytes == sum(ref[n].numel() * ref[n].element_size() for n in names)
+    assert full.d2h_bytes == r.d2h_bytes + ref["packed"].numel() * 2
+    assert r.h2d_bytes == t * d * 2
+    with pytest.raises(ValueError):
+        HostRouter(t, d, w, k, download=("idx", "nonsense"))
