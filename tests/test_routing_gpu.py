@@ -46,6 +46,36 @@ def test_topk_select_bit_exact(ops, t, e, k, dtype, ties):
     assert ops.read_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_topk_select_16bit_special_values(ops, dtype):
+    """The key-based kernel for 16-bit logits: -inf rows select in index order, +inf wins, -0 ties +0
+    (lower index first), all-equal rows pick the first columns; E = 8 ... 1024, k = 1 ... 8."""
+    logits = torch.full((5, 64), float("-inf"), dtype=dtype)
+    logits[1, 7] = 1.0
+    logits[2, 63] = float("inf")
+    logits[3, :] = 0.0
+    logits[4, :] = -0.0
+    logits[4, 9] = 0.0
+    logits[4, 3] = -1.0
+    idx, gates = ops.topk_select(logits.cuda(), 2)
+    np.testing.assert_array_equal(idx.cpu().numpy(), [[0, 1], [7, 0], [63, 0], [0, 1], [0, 1]])
+    np.testing.assert_allclose(gates.cpu().numpy()[3:], 0.5)
+    np.testing.assert_allclose(gates.cpu().numpy()[1], [1.0, 0.0])
+    for t, e, k in [(100, 8, 2), (33, 1024, 8), (257, 128, 4), (64, 40, 1), (1000, 512, 3)]:
+        g = torch.Generator().manual_seed(t + e)
+        v = (torch.round(torch.randn(t, e, generator=g) * 4) / 4).to(dtype)  # many ties
+        idx, gates = ops.topk_select(v.cuda(), k)
+        ref_idx, ref_g, _ = oracle.topk_select(v.float().numpy(), k)
+        np.testing.assert_array_equal(idx.cpu().numpy(), ref_idx.astype(np.int32))
+        np.testing.assert_allclose(gates.cpu().numpy(), ref_g, rtol=1e-5, atol=1e-7)
+    # a view that starts 2 bytes into an allocation is not 16-byte aligned: the generic kernel takes it
+    base = torch.randn(65 * 64 + 8, generator=torch.Generator().manual_seed(1)).to(dtype).cuda()
+    off = base[1:1 + 64 * 64].view(64, 64)
+    idx, _ = ops.topk_select(off, 2)
+    ref_idx, _, _ = oracle.topk_select(off.float().cpu().numpy(), 2)
+    np.testing.assert_array_equal(idx.cpu().numpy(), ref_idx.astype(np.int32))
+
+
 def test_topk_select_handles_infinities(ops):
     logits = torch.full((4, 64), float("-inf"))
     logits[1, 7] = 1.0
