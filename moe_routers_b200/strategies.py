@@ -16,10 +16,14 @@ def route(strategy: str, x: torch.Tensor, w_router: torch.Tensor, top_k: int, *,
     """Routing of `x` under `strategy`.  Returns a dict with idx / gates and, for the strategies that
     permute (all but masked_matmul), counts / offsets / packed / row_route / route_row."""
     e = w_router.size(0)
-    if strategy == "fused_select":
-        return ops.route_fused(x, w_router, top_k, skew_experts=skew_experts, skew_bias=skew_bias)
     if strategy not in STRATEGIES:
         raise ValueError(f"Unknown strategies: {[strategy]}. Valid: {STRATEGIES}")
+    if strategy == "fused_select":
+        return ops.route_fused(x, w_router, top_k, skew_experts=skew_experts, skew_bias=skew_bias)
+    if strategy == "naive_topk":
+        # the same selection as fused_select (top-k of the logits, lowest index wins ties) with the
+        # logits written out as well, as torch.topk on materialised logits would need them
+        return ops.route_fused(x, w_router, top_k, skew_experts=skew_experts, skew_bias=skew_bias, return_logits=True)
     idx, gates, logits = ops.router_gemm_select(x, w_router, top_k, skew_experts=skew_experts,
                                                 skew_bias=skew_bias, return_logits=True)
     if strategy == "sinkhorn":

@@ -2,7 +2,7 @@
 
 TEST / BENCHMARK INFRASTRUCTURE ONLY (see the package docstring).
 
-    python -m oracle.build_ref [--reference /path/to/moe-routers]
+    python -m oracle.build_ref --reference /path/to/moe-routers
 
 The reference's CPU path is pure Python (`bench_router.py --device cpu`, lines 484-505, with
 `models/decoder_moe.py` for the routers), so "building" it means placing its four unmodified files
@@ -38,7 +38,7 @@ def staged() -> bool:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of santiweide/moe-routers")
     a = ap.parse_args()
     out = stage(a.reference)
     print(out if out else f"reference checkout not found at {a.reference}: nothing staged")
