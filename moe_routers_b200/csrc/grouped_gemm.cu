@@ -67,6 +67,8 @@ struct GParams {
   int stage_area;           // bytes reserved for the stage ring (the larger of the two layouts)
   int producers;            // warps that issue TMA copies with single-tile units (1..2)
   int m64;                  // 1: a last tile of <= 64 rows runs as UMMA M=64; 0: every tile is 128 rows
+  int cta2_min_avg;         // two-CTA kernel when the experts hold at least this many rows on average (0: never)
+  int stages_cta2;          // pipeline depth of the two-CTA kernel
   int32_t* status;
 };
 
@@ -75,6 +77,13 @@ constexpr int kStageWarpBytes = 32 * kStageRowBytes;
 
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+
+// Whether this call runs on the two-CTA kernel: decided on the device from the number of rows
+// actually routed (the host only knows the capacity of the row buffer); both kernels of a call
+// evaluate it and exactly one of them does the work.
+__device__ __forceinline__ bool cta2_mode(const GParams& p, int routed) {
+  return p.cta2_min_avg > 0 && (long long)routed >= (long long)p.cta2_min_avg * p.experts;
+}
 
 // Work unit id -> (expert, n tile, first row, whether the unit has a second 128-row tile).
 // Units [0, n_a * n_tiles) are class A: single 128-row tiles, or in pair mode the full two-tile
@@ -95,7 +104,7 @@ __device__ __forceinline__ int last_not_above(const int32_t* pre, int n, int n_t
   return lo;
 }
 __device__ __forceinline__ Unit decode_unit(const int32_t* s_a, const int32_t* s_b, const int32_t* offsets, int experts,
-                                            int n_tiles, int pair, int t) {
+                                            int rows, int n_tiles, int pair, int t) {
   Unit u;
   const int total_a = s_a[experts] * n_tiles;
   if (t < total_a) {
@@ -109,7 +118,8 @@ __device__ __forceinline__ Unit decode_unit(const int32_t* s_a, const int32_t* s
     const int tb = t - total_a;
     u.e = last_not_above(s_b, experts, n_tiles, tb);
     u.nt = tb - s_b[u.e] * n_tiles;
-    u.row0 = offsets[u.e] + (s_a[u.e + 1] - s_a[u.e]) * 2 * kBM;  // after the expert's full pairs
+    const int cnt = min(offsets[u.e + 1], rows) - offsets[u.e];
+    u.row0 = offsets[u.e] + ((cnt + kBM - 1) / kBM - 1) * kBM;  // the expert's last tile
     u.two = false;
   }
   return u;
@@ -189,6 +199,89 @@ __device__ __forceinline__ void store_staged_rows(const uint8_t* stage, uint16_t
   }
 }
 
+// What an epilogue warp needs to know about itself.  Warp w of the eight reads TMEM lanes
+// 32*(w%4)..; the two warps of a lane quarter split the tile's columns (dense output, >= 64 columns),
+// otherwise the second warp of a quarter only takes part in the barriers.
+struct EpiCtx {
+  int q, lane, col_half, out_bn;
+  bool split, swiglu;
+  uint8_t* s_stage;
+};
+__device__ __forceinline__ EpiCtx make_epi_ctx(const GParams& p, int warp, int lane, uint8_t* s_stage) {
+  EpiCtx c;
+  c.q = warp & 3;
+  c.lane = lane;
+  c.col_half = (warp - 2) >> 2;  // 0: warps 2..5, 1: warps 6..9
+  c.swiglu = p.act == MOE_ACT_SWIGLU;
+  c.out_bn = c.swiglu ? p.bn / 2 : p.bn;  // output columns per tile
+  c.split = p.c_rows == nullptr && c.out_bn >= 64;
+  c.s_stage = s_stage;
+  return c;
+}
+
+// Which rows and columns of a tile a TMEM lane holds.
+enum : int {
+  kAccM128 = 0,    // UMMA M=128 (or one CTA's half of a two-CTA M=256): lane = row, all columns
+  kAccM64 = 1,     // as kAccM128, but a tile that holds at most 64 rows was issued as UMMA M=64: 16 rows in each
+                   // 32-lane quarter (lanes 0..15 of the quarter)
+  kAccPairM128 = 2 // one CTA's half (64 rows) of a two-CTA M=128: lanes 0..63 hold the rows' columns 0..N/2-1,
+                   // lanes 64..127 the same rows' columns N/2..N-1, both at accumulator columns 0..N/2-1
+};
+
+// One accumulator (`tmem_acc`: TMEM address of its first column, lane 0) -> output rows row0.. of
+// expert e, columns of n tile nt; rows at or past seg_end are masked.
+__device__ __forceinline__ void epilogue_tile(const GParams& p, const EpiCtx& c, uint32_t tmem_acc, int e, int nt,
+                                              int row0, int seg_end, int acc_layout) {
+  const int out_bn = c.out_bn, lane = c.lane, q = c.q;
+  const bool swiglu = c.swiglu;
+  // accumulator columns this lane holds, and the output column (inside the n tile) of the first
+  const int cols = acc_layout == kAccPairM128 ? out_bn / 2 : out_bn;
+  const int col_off = acc_layout == kAccPairM128 ? (q >> 1) * (out_bn / 2) : 0;
+  const int c_lo = c.split ? c.col_half * (cols / 2) : 0;
+  const int c_hi = c.split ? c_lo + cols / 2 : (c.col_half == 0 ? cols : 0);
+  if (c_lo >= c_hi) return;
+  // bias of expert e: main columns at nt*out_bn, SwiGLU up columns n_out further
+  const int n_w = swiglu ? 2 * p.n_out : p.n_out;
+  const uint16_t* brow = p.bias ? p.bias + (size_t)e * n_w + (size_t)nt * out_bn + col_off : nullptr;
+  int trow = q * 32 + lane;  // row of the tile held by this thread's TMEM lane
+  bool lane_used = true;
+  if (acc_layout == kAccM64 && seg_end - row0 <= 64) {
+    trow = q * 16 + lane;
+    lane_used = lane < 16;
+  } else if (acc_layout == kAccPairM128) {
+    trow = (q & 1) * 32 + lane;
+  }
+  const int grow = row0 + trow;
+  const bool valid = lane_used && grow < seg_end && grow >= 0;
+  const uint32_t acc = tmem_acc + ((uint32_t)(q * 32) << 16);
+  const float scale = (valid && p.row_scale != nullptr) ? p.row_scale[grow] : 1.f;
+  uint16_t* crow;
+  if (p.c_rows == nullptr) crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn + col_off;
+  else crow = (valid ? p.c_rows[grow] : nullptr) + (size_t)nt * out_bn + col_off;
+  if (p.c_rows != nullptr && out_bn % 64 == 0) {
+    uint8_t* stage = c.s_stage + q * kStageWarpBytes;
+    uint16_t* mine = reinterpret_cast<uint16_t*>(stage + lane * kStageRowBytes);
+    for (int c0 = c_lo; c0 < c_hi; c0 += 64) {
+#pragma unroll
+      for (int hh = 0; hh < 64; hh += 32)
+        epilogue_chunk<32>(acc + (uint32_t)(c0 + hh), acc + (uint32_t)(out_bn + c0 + hh), swiglu, p.act, scale, true,
+                           mine + hh, brow ? brow + c0 + hh : nullptr,
+                           (brow && swiglu) ? brow + p.n_out + c0 + hh : nullptr, p.bf16 != 0);
+      __syncwarp();
+      store_staged_rows(stage, crow, valid, c0, lane);
+      __syncwarp();
+    }
+  } else if (out_bn % 64 == 0 || (!c.split && out_bn % 32 == 0)) {
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32)
+      epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0,
+                         brow ? brow + c0 : nullptr, (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
+  } else {
+    for (int c0 = c_lo; c0 < c_hi; c0 += 16)
+      epilogue_chunk<16>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid, crow + c0,
+                         brow ? brow + c0 : nullptr, (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
+  }
+}
+
 // The weight boxes of one stage: f(byte offset inside the stage's B area, tensor-map coordinates).
 template <typename F>
 __device__ __forceinline__ void for_each_weight_box(const GParams& p, int BN, bool swiglu, int kb, int nt, int e, F&& f) {
@@ -224,6 +317,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   // Pair mode is chosen here, from the number of rows actually routed (the host only knows the
   // capacity of the row buffer): every thread reads the same total and takes the same branch.
   const int routed = min(p.offsets[p.experts], p.rows);
+  if (cta2_mode(p, routed)) return;  // grouped_gemm_cta2_kernel, launched next, does this call's work
   const int pair = (p.pair_min_avg > 0 && (long long)routed >= (long long)p.pair_min_avg * p.experts) ? 1 : 0;
   const int n_stages = pair ? p.stages_pair : p.stages;
   const int PM = pair ? 2 : 1;            // 128-row tiles per work unit
@@ -309,23 +403,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int pw = warp == 0 ? 0 : warp - 9;
     const int producers = pair ? 1 : min(p.producers, n_stages);
     if (lane == 0 && pw < producers) {
-      uint32_t it = 0;  // k-block counter across tiles
+      int s = 0;        // stage and the parity of its use, advanced without divisions (this thread is
+      uint32_t ph = 0;  // on the critical path of its stages)
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.n_tiles, pair, t);
+        const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.rows, p.n_tiles, pair, t);
         const int e = u.e, nt = u.nt, row0 = u.row0;
         const bool two = u.two;  // the unit has a second tile
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = (int)(it % (uint32_t)n_stages);
-          if (s % producers != pw) continue;
-          const uint32_t ph = (it / (uint32_t)n_stages) & 1u;
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1)) { ok = false; break; }
-          mbar_expect_tx(full0 + 8 * s, (uint32_t)(kABytes * (two ? 2 : 1) + b_bytes));
-          tma_load_2d(smem_u32(sA + (size_t)s * a_stage), &tmap_a, full0 + 8 * s, kb * kBK, row0);
-          if (two) tma_load_2d(smem_u32(sA + (size_t)s * a_stage + kABytes), &tmap_a, full0 + 8 * s, kb * kBK, row0 + kBM);
-          const uint32_t sb = smem_u32(sB + (size_t)s * b_bytes);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          const int s_now = s;
+          const uint32_t ph_now = ph;
+          if (++s == n_stages) { s = 0; ph ^= 1u; }
+          if (producers == 2 && (s_now & 1) != pw) continue;
+          if (!mbar_wait(empty0 + 8 * s_now, ph_now ^ 1u, p.status, 1)) { ok = false; break; }
+          mbar_expect_tx(full0 + 8 * s_now, (uint32_t)(kABytes * (two ? 2 : 1) + b_bytes));
+          tma_load_2d(smem_u32(sA + (size_t)s_now * a_stage), &tmap_a, full0 + 8 * s_now, kb * kBK, row0);
+          if (two) tma_load_2d(smem_u32(sA + (size_t)s_now * a_stage + kABytes), &tmap_a, full0 + 8 * s_now, kb * kBK, row0 + kBM);
+          const uint32_t sb = smem_u32(sB + (size_t)s_now * b_bytes);
           for_each_weight_box(p, BN, swiglu, kb, nt, e, [&](uint32_t ofs, int c0, int c1, int c2) {
-            tma_load_3d(sb + ofs, &tmap_w, full0 + 8 * s, c0, c1, c2);
+            tma_load_3d(sb + ofs, &tmap_w, full0 + 8 * s_now, c0, c1, c2);
           });
         }
       }
@@ -336,11 +432,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (lane == 0) {
       const uint32_t idesc128 = make_idesc_f16(kBM, BN, p.bf16, 0, p.w_kn);
       const uint32_t idesc64 = make_idesc_f16(64, BN, p.bf16, 0, p.w_kn);
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       int local = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-        const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.n_tiles, pair, t);
+        const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.rows, p.n_tiles, pair, t);
         const int seg_end = min(p.offsets[u.e + 1], p.rows);
         const int row0 = u.row0;
         const bool two = u.two;
@@ -354,9 +451,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (pair && !mbar_wait(tempty0 + 8, par ^ 1u, p.status, 4)) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = (int)(it % (uint32_t)n_stages);
-          const uint32_t ph = (it / (uint32_t)n_stages) & 1u;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait(full0 + 8 * s, ph, p.status, 2)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + (size_t)s * a_stage);
@@ -380,6 +475,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
           umma_commit(empty0 + 8 * s);
+          if (++s == n_stages) { s = 0; ph ^= 1u; }
         }
         umma_commit(tfull0 + 8 * ab);
         if (pair) umma_commit(tfull0 + 8);
@@ -388,69 +484,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncwarp();
   } else {
     // ------------------------------ epilogue -----------------------------------
-    const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    // Two warps share a lane quarter and split the tile's columns (dense output, >= 64 columns);
-    // otherwise the second warp of a quarter only takes part in the barriers.
-    const bool split = p.c_rows == nullptr && (swiglu ? BN / 2 : BN) >= 64;
-    const int col_half = (warp - 2) >> 2;   // 0: warps 2..5, 1: warps 6..9
+    const EpiCtx ec = make_epi_ctx(p, warp, lane, s_stage);
     int local = 0;
-    const int out_bn = swiglu ? BN / 2 : BN;  // output columns per tile
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-      const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.n_tiles, pair, t);
+      const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.rows, p.n_tiles, pair, t);
       const int e = u.e, nt = u.nt;
       const int seg_end = min(p.offsets[e + 1], p.rows);
-      // bias of expert e: main columns at nt*out_bn, SwiGLU up columns n_out further
-      const int n_w = swiglu ? 2 * p.n_out : p.n_out;
-      const uint16_t* brow = p.bias ? p.bias + (size_t)e * n_w + (size_t)nt * out_bn : nullptr;
       for (int h = 0; h < PM; ++h) {
         const int ab = pair ? h : (local & 1);
         const uint32_t par = pair ? ((uint32_t)local & 1u) : (((uint32_t)local >> 1) & 1u);
         const int row0 = u.row0 + h * kBM;
         if (!mbar_wait(tfull0 + 8 * ab, par, p.status, 3)) { ok = false; break; }
         tc_fence_after();
-        const int c_lo = split ? col_half * (out_bn / 2) : 0;
-        const int c_hi = split ? c_lo + out_bn / 2 : (col_half == 0 ? out_bn : 0);
-        if ((h == 0 || u.two) && c_lo < c_hi) {  // (the second accumulator of a single-tile unit holds nothing)
-          int trow = q * 32 + lane;  // row of the tile held by this thread's TMEM lane
-          bool lane_used = true;
-          if (p.m64 && seg_end - row0 <= 64) {
-            // the M=64 accumulator keeps 16 rows in each 32-lane TMEM quarter (lanes 0..15 of the quarter)
-            trow = q * 16 + lane;
-            lane_used = lane < 16;
-          }
-          const int grow = row0 + trow;
-          const bool valid = lane_used && grow < seg_end && grow >= 0;
-          const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
-          const float scale = (valid && p.row_scale != nullptr) ? p.row_scale[grow] : 1.f;
-          uint16_t* crow;
-          if (p.c_rows == nullptr) crow = p.c + (size_t)(valid ? grow : 0) * p.n_out + (size_t)nt * out_bn;
-          else crow = (valid ? p.c_rows[grow] : nullptr) + (size_t)nt * out_bn;
-          if (p.c_rows != nullptr && out_bn % 64 == 0) {
-            uint8_t* stage = s_stage + q * kStageWarpBytes;
-            uint16_t* mine = reinterpret_cast<uint16_t*>(stage + lane * kStageRowBytes);
-            for (int c0 = c_lo; c0 < c_hi; c0 += 64) {
-#pragma unroll
-              for (int hh = 0; hh < 64; hh += 32)
-                epilogue_chunk<32>(acc + (uint32_t)(c0 + hh), acc + (uint32_t)(out_bn + c0 + hh), swiglu, p.act, scale,
-                                   true, mine + hh, brow ? brow + c0 + hh : nullptr,
-                                   (brow && swiglu) ? brow + p.n_out + c0 + hh : nullptr, p.bf16 != 0);
-              __syncwarp();
-              store_staged_rows(stage, crow, valid, c0, lane);
-              __syncwarp();
-            }
-          } else if (out_bn % 64 == 0 || (!split && out_bn % 32 == 0)) {
-            for (int c0 = c_lo; c0 < c_hi; c0 += 32)
-              epilogue_chunk<32>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid,
-                                 crow + c0, brow ? brow + c0 : nullptr,
-                                 (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
-          } else {
-            for (int c0 = c_lo; c0 < c_hi; c0 += 16)
-              epilogue_chunk<16>(acc + (uint32_t)c0, acc + (uint32_t)(out_bn + c0), swiglu, p.act, scale, valid,
-                                 crow + c0, brow ? brow + c0 : nullptr,
-                                 (brow && swiglu) ? brow + p.n_out + c0 : nullptr, p.bf16 != 0);
-          }
-        }
+        // (the second accumulator of a single-tile unit holds nothing)
+        if (h == 0 || u.two)
+          epilogue_tile(p, ec, tmem_base + (uint32_t)(ab * BN), e, nt, row0, seg_end, p.m64 ? kAccM64 : kAccM128);
         tc_fence_before();
         mbar_arrive(tempty0 + 8 * ab);  // this thread is done reading the accumulator
       }
@@ -462,6 +511,259 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Two-CTA kernel (experts with many rows, 256 accumulator columns).  A cluster of two CTAs works on a
+// unit of 256 rows x one n tile of one expert with `tcgen05.mma.cta_group::2`: D = 256 x 256 per
+// instruction, rows 0..127 in the even CTA's TMEM and rows 128..255 in the odd CTA's.  CTA r loads its
+// own 128 rows of A and ITS HALF of the weight tile (128 of the 256 accumulator columns; the tensor
+// core reads the other half from the other CTA's shared memory), so the operand bytes per FLOP are
+// those of a 256 x 256 tile while every CTA keeps two 256-column accumulators: the epilogue of unit
+// i (GELU costs about 9,000 cycles per 128 x 256 tile, more than a quarter of the tile's tensor time)
+// runs entirely under the main loop of unit i+1, which two-tile units of one CTA cannot do (their two
+// accumulators belong to one unit; the MMA thread then idles a fifth of the time).
+// The copies are ordinary TMA loads of this GPU's memory into the issuing CTA's own shared memory;
+// only their completion is signalled to the even CTA's barrier.  The even CTA's thread issues the
+// MMAs; its commits arrive on the barriers of both CTAs.
+// Warp roles (416 threads): warps 0, 10, 11, 12 issue the TMA copies (copies of one thread are served
+// one after another, so the operand boxes are spread over four), warp 1 owns TMEM and, in the even
+// CTA, issues the MMAs, warps 2..9 are the epilogue of the CTA's own 128 rows.
+// An expert with an odd number of 128-row tiles ends with a unit of one tile, issued as a two-CTA
+// M=128 (64 rows per CTA, half the tensor time; the accumulator then holds each row's two column
+// halves on lanes l and l+64).  SwiGLU pairs a row's gate and up columns inside one lane, so there the
+// last unit stays M=256 with its second half past the expert's rows, computed and masked.  The
+// one-tile units are listed after all full ones, so the round-robin hands every cluster the same mix.
+constexpr int kCThreads = 416;
+// A stage holds two 64-wide k blocks of each operand (A block 0 | A block 1 | weight-half block 0 |
+// weight-half block 1, 16 KiB each): the commit that frees a stage costs the issuing thread about as
+// much as four MMAs, and with one k block per stage (six 32 KiB stages) the kernel measured 20 %
+// slower, bound by that thread.
+constexpr int kCKH = 2;
+constexpr int kCStageBytes = kCKH * 2 * kABytes;
+constexpr int kCRows = 2 * kBM;            // rows per unit
+
+struct CUnit {
+  int e, nt, row0;
+  bool one;  // the expert's odd last tile
+};
+// Inside a class, units are ordered by expert, then n tile, then row group, so clusters that run at
+// the same time share weight tiles through L2.  s_a[e] / s_b[e] = full / one-tile units (per n tile)
+// of experts < e.
+__device__ __forceinline__ CUnit decode_cta2(const int32_t* s_a, const int32_t* s_b, const GParams& p, int t) {
+  CUnit u;
+  const int total_a = s_a[p.experts] * p.n_tiles;
+  if (t < total_a) {
+    u.e = last_not_above(s_a, p.experts, p.n_tiles, t);
+    const int per = s_a[u.e + 1] - s_a[u.e];
+    const int local = t - s_a[u.e] * p.n_tiles;
+    u.nt = local / per;
+    u.row0 = p.offsets[u.e] + (local % per) * kCRows;
+    u.one = false;
+  } else {
+    const int tb = t - total_a;
+    u.e = last_not_above(s_b, p.experts, p.n_tiles, tb);
+    u.nt = tb - s_b[u.e] * p.n_tiles;
+    u.row0 = p.offsets[u.e] + (s_a[u.e + 1] - s_a[u.e]) * kCRows;  // after the expert's full units
+    u.one = true;
+  }
+  return u;
+}
+
+__global__ void __launch_bounds__(kCThreads, 1)
+grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
+                         const __grid_constant__ CUtensorMap tmap_w, const GParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  // every CTA reads the same total and takes the same branch (no barrier has been touched yet)
+  if (!cta2_mode(p, min(p.offsets[p.experts], p.rows))) return;
+  if ((smem_u32(smem) & 1023u) != 0u) {  // the same in both CTAs of a pair
+    record_error(p.status, kErrBadIndex | 0xfd);
+    return;
+  }
+  constexpr int BN = 256;
+  constexpr int KH = kCKH;
+  const int n_stages = p.stages_cta2;
+  const int kblocks = (p.kblocks + KH - 1) / KH;  // stages per unit
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + (size_t)n_stages * kCStageBytes);
+  // full[kMaxStages] (used in the even CTA), empty[kMaxStages], tmem_full[2], tmem_empty[2] (even CTA)
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);
+  int32_t* s_mt = reinterpret_cast<int32_t*>(s_tmem + 4);  // [experts + 1] full units before each expert
+  int32_t* s_mb = s_mt + p.experts + 1;                    // [experts + 1] one-tile units before each expert
+  uint8_t* s_stage = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(s_mb + p.experts + 1) + 15) & ~static_cast<uintptr_t>(15));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: the CTA that issues the MMAs
+  const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const uint32_t full0 = smem_u32(s_bar);
+  const uint32_t empty0 = smem_u32(s_bar + kMaxStages);
+  const uint32_t tfull0 = smem_u32(s_bar + 2 * kMaxStages);
+  const uint32_t tempty0 = smem_u32(s_bar + 2 * kMaxStages + 2);
+  constexpr uint32_t kTmemCols = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);   // the even CTA's producer arrives with the byte count of both CTAs
+      mbar_init(empty0 + 8 * s, 1);  // one commit per use
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull0 + 8 * b, 1);
+      mbar_init(tempty0 + 8 * b, 2 * kEpiThreads);  // every epilogue thread of both CTAs arrives
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_a64);
+    prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    // each CTA allocates all of its own TMEM, so both get the same base address
+    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 2) {
+    int carry_a = 0, carry_b = 0;
+    for (int eb = 0; eb < p.experts; eb += 32) {
+      const int e = eb + lane;
+      int ca = 0, cb = 0;
+      if (e < p.experts) {
+        const int lo = p.offsets[e], hi = min(p.offsets[e + 1], p.rows);
+        const int tiles = hi > lo ? (hi - lo + kBM - 1) / kBM : 0;
+        ca = tiles / 2;
+        cb = tiles & 1;
+      }
+      int ia = ca, ib = cb;
+#pragma unroll
+      for (int ofs = 1; ofs < 32; ofs <<= 1) {
+        const int na = __shfl_up_sync(0xffffffffu, ia, ofs);
+        const int nb = __shfl_up_sync(0xffffffffu, ib, ofs);
+        if (lane >= ofs) { ia += na; ib += nb; }
+      }
+      if (e < p.experts) { s_mt[e] = carry_a + ia - ca; s_mb[e] = carry_b + ib - cb; }
+      carry_a += __shfl_sync(0xffffffffu, ia, 31);
+      carry_b += __shfl_sync(0xffffffffu, ib, 31);
+    }
+    if (lane == 0) { s_mt[p.experts] = carry_a; s_mb[p.experts] = carry_b; }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before any copy or arrival names them
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  const int total_units = (s_mt[p.experts] + s_mb[p.experts]) * p.n_tiles;
+  const bool swiglu = p.act == MOE_ACT_SWIGLU;
+
+  if (warp == 0 || warp >= 10) {
+    // ------------------------------ TMA producers ------------------------------
+    // Producers 0/1 copy the two k blocks of this CTA's rows of A, producers 2/3 those of its half of
+    // the weight tile.  Every producer waits for the stage to be free in its own CTA; the bytes of both CTAs complete on the
+    // even CTA's `full` barrier, armed by the even CTA's producer of the stage's first A block.
+    const int op = warp == 0 ? 0 : warp - 9;
+    const int which = op >> 1, sub = op & 1;
+    if (lane == 0) {
+      int s = 0;         // stage and the parity of its use, advanced without divisions
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = cluster; t < total_units && ok; t += n_clusters) {
+        const CUnit u = decode_cta2(s_mt, s_mb, p, t);
+        const bool m128 = u.one && !swiglu;  // one tile as a two-CTA M=128: 64 rows of A per CTA
+        // first weight row (column, for [K, N] weights) of this CTA's half: SwiGLU tiles hold the gate
+        // columns in the even CTA's half and the up columns in the odd CTA's
+        const int n0 = swiglu ? (int)rank * p.n_out + u.nt * (BN / 2) : u.nt * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1)) { ok = false; break; }
+          const uint32_t full_even = map_to_cta(full0 + 8 * s, 0);
+          const int h = sub;  // k block of the stage
+          const uint32_t st = smem_u32(smem + (size_t)s * kCStageBytes) + (uint32_t)((which * KH + h) * kABytes);
+          const int k0 = (kb * KH + h) * kBK;
+          if (which == 0 && h == 0 && rank == 0)
+            mbar_expect_tx(full0 + 8 * s, (uint32_t)(m128 ? 2 * KH * (kABytes / 2 + kABytes) : 2 * kCStageBytes));
+          if (which == 0) {
+            if (m128) tma_load_2d_pair(st, &tmap_a64, full_even, k0, u.row0 + (int)rank * (kBM / 2));
+            else tma_load_2d_pair(st, &tmap_a, full_even, k0, u.row0 + (int)rank * kBM);
+          } else if (!p.w_kn) {
+            tma_load_3d_pair(st, &tmap_w, full_even, k0, n0, u.e);  // 128 rows of the K-major tile
+          } else {
+            // weights [E, K, Nw]: two boxes of 64 (N) x 64 (K)
+            tma_load_3d_pair(st, &tmap_w, full_even, n0, k0, u.e);
+            tma_load_3d_pair(st + 8192u, &tmap_w, full_even, n0 + 64, k0, u.e);
+          }
+          if (++s == n_stages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA) ----------------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc256 = make_idesc_f16(2 * kBM, BN, p.bf16, 0, p.w_kn);
+      const uint32_t idesc128 = make_idesc_f16(kBM, BN, p.bf16, 0, p.w_kn);
+      const int total_a = s_mt[p.experts] * p.n_tiles;
+      int s = 0;
+      uint32_t ph = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = cluster; t < total_units && ok; t += n_clusters, ++local) {
+        const uint32_t idesc = (t >= total_a && !swiglu) ? idesc128 : idesc256;
+        const int ab = local & 1;  // units alternate between the two accumulators
+        const uint32_t par = ((uint32_t)local >> 1) & 1u;
+        if (!mbar_wait(tempty0 + 8 * ab, par ^ 1u, p.status, 4)) break;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(full0 + 8 * s, ph, p.status, 2)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * kCStageBytes);
+          const uint32_t b_addr = a_addr + KH * kABytes;
+#pragma unroll
+          for (int h = 0; h < KH; ++h) {
+            const uint64_t adesc = make_desc_kmajor_sw128(a_addr + (uint32_t)(h * kABytes));
+#pragma unroll
+            for (int k = 0; k < kBK / kUK; ++k) {
+              uint64_t bdesc;
+              if (!p.w_kn) bdesc = make_desc_kmajor_sw128(b_addr + (uint32_t)(h * kABytes)) + 2 * k;  // +32 B along K
+              else bdesc = make_desc_mnmajor_sw128(b_addr + (uint32_t)(h * kABytes) + (uint32_t)k * 2048u, 8192u);
+              umma_f16_pair(acc, adesc + 2 * k, bdesc, idesc, (uint32_t)((kb | h | k) != 0));
+            }
+          }
+          umma_commit_pair(empty0 + 8 * s, 3);  // the stage is free in both CTAs
+          if (++s == n_stages) { s = 0; ph ^= 1u; }
+        }
+        umma_commit_pair(tfull0 + 8 * ab, 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue (both CTAs) -----------------------
+    const EpiCtx ec = make_epi_ctx(p, warp, lane, s_stage);
+    const uint32_t tempty_even = map_to_cta(tempty0, 0);
+    int local = 0;
+    for (int t = cluster; t < total_units; t += n_clusters, ++local) {
+      const CUnit u = decode_cta2(s_mt, s_mb, p, t);
+      const int seg_end = min(p.offsets[u.e + 1], p.rows);
+      const int ab = local & 1;
+      if (!mbar_wait(tfull0 + 8 * ab, ((uint32_t)local >> 1) & 1u, p.status, 3)) break;
+      tc_fence_after();
+      if (u.one && !swiglu)
+        epilogue_tile(p, ec, tmem_base + (uint32_t)(ab * BN), u.e, u.nt, u.row0 + (int)rank * (kBM / 2), seg_end, kAccPairM128);
+      else
+        epilogue_tile(p, ec, tmem_base + (uint32_t)(ab * BN), u.e, u.nt, u.row0 + (int)rank * kBM, seg_end, kAccM128);
+      tc_fence_before();
+      mbar_arrive_cluster(tempty_even + 8 * ab);  // this thread is done reading the accumulator
+    }
+    __syncwarp();
+  }
+
+  // no CTA leaves (or frees TMEM) while the other may still read its shared memory or signal its barriers
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -555,16 +857,25 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
     p.stages_pair = stages_pair;
     p.pair_min_avg = (pair_on && p.bn == 256 && stages_pair >= 2) ? 4 * kBM : 0;
   }
-  size_t stage_area = (size_t)stages * stage_single;
-  if (p.pair_min_avg && (size_t)p.stages_pair * stage_pair > stage_area) stage_area = (size_t)p.stages_pair * stage_pair;
-  p.stage_area = (int)stage_area;
-  const size_t smem = stage_area + fixed;
-
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
   if (sm_margin > 0 && sm_margin < sms) sms -= sm_margin;
+  {
+    // The two-CTA kernel takes the calls whose experts hold 512 rows or more on average (it replaces
+    // the two-tile units of one CTA there); MOE_B200_CTA2=0 in the environment disables it.
+    static const int cta2_on = [] { const char* v = getenv("MOE_B200_CTA2"); return (v && v[0] == '0') ? 0 : 1; }();
+    int stages_cta2 = (227 * 1024 - fixed) / kCStageBytes;
+    if (stages_cta2 > kMaxStages) stages_cta2 = kMaxStages;
+    p.stages_cta2 = stages_cta2;
+    p.cta2_min_avg = (cta2_on && p.bn == 256 && stages_cta2 >= 2 && sms >= 2) ? 4 * kBM : 0;
+  }
+  size_t stage_area = (size_t)stages * stage_single;
+  if (p.pair_min_avg && (size_t)p.stages_pair * stage_pair > stage_area) stage_area = (size_t)p.stages_pair * stage_pair;
+  p.stage_area = (int)stage_area;
+  const size_t smem = stage_area + fixed;
+
   // upper bound of the tile count known on the host: every expert may add one partial m tile
   const long long max_tiles = ((long long)rows / kBM + experts) * p.n_tiles;
   const int grid = (int)(max_tiles < sms ? max_tiles : sms);
@@ -572,7 +883,39 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
   cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_grouped_gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   grouped_gemm_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tmap_a, tmap_w, p);
-  return check_launch("grouped_gemm_kernel");
+  rc = check_launch("grouped_gemm_kernel");
+  if (rc != MOE_OK || p.cta2_min_avg == 0) return rc;
+
+  // The two-CTA kernel: whichever of the two kernels the routed row count selects does the work, the
+  // other returns at once (the choice needs the offsets, which only the device has).
+  CUtensorMap tmap_wq = tmap_w, tmap_a64;
+  rc = encode_tmap_2d(&tmap_a64, a, (uint64_t)rows, (uint64_t)K, (uint64_t)K * 2, kBK, kBM / 2);
+  if (rc != MOE_OK) return rc;
+  if (!p.w_kn && !swiglu) {
+    rc = encode_tmap_3d(&tmap_wq, w, (uint64_t)experts, (uint64_t)n_w, (uint64_t)K, (uint64_t)K * 2,
+                        (uint64_t)stride_w * 2, kBK, 128);
+    if (rc != MOE_OK) return rc;
+  }
+  const size_t smem_q = (size_t)p.stages_cta2 * kCStageBytes + fixed;
+  const long long max_units = ((long long)rows / kCRows + experts) * p.n_tiles;
+  const int clusters = (int)(max_units < sms / 2 ? max_units : sms / 2);
+  e = cudaFuncSetAttribute(grouped_gemm_cta2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q);
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_grouped_gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kCThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem_q;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, grouped_gemm_cta2_kernel, tmap_a, tmap_a64, tmap_wq, p);
+  if (e != cudaSuccess) return fail(MOE_ERR_LAUNCH, "moe_grouped_gemm: cluster launch: %s", cudaGetErrorString(e));
+  return check_launch("grouped_gemm_cta2_kernel");
 }
 }  // namespace
 }  // namespace moe

@@ -72,6 +72,13 @@ CASES = [
     ([385, 640, 1, 1030], 320, 256, "kn", None),
     ([600, 256, 300, 1000], 128, 128, "nk", "swiglu"),
     ([257, 513, 769, 564], 192, 256, "kn", "swiglu"),
+    # the same class of shapes on the two-CTA kernel: units of 512 rows, every remainder (1..3 tiles,
+    # partial tiles, a one-row expert, an empty expert), one k block, K not a multiple of 64, many units
+    ([129, 1280, 385, 900], 72, 256, "nk", None),
+    ([1, 2047, 640, 0], 256, 256, "kn", "gelu"),
+    ([1024], 64, 256, "nk", None),
+    ([2048, 2048], 128, 1024, "nk", "silu"),
+    ([511, 513, 1025, 1023], 136, 512, "kn", None),
 ]
 
 
