@@ -56,6 +56,14 @@ WORKLOAD = "fused_select T=4096 d_model=4096 E=64 top_k=2 fp16, +2.0 skew on exp
 METRIC = "routed tokens/s per MoE layer"
 
 
+_T0 = time.time()
+
+
+def _progress(msg: str) -> None:
+    """Section marks with the seconds since start, on stderr (the JSON line owns stdout)."""
+    print(f"[bench {time.time() - _T0:7.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -436,6 +444,7 @@ def main_ours(args):
         del hr
         return rec
 
+    _progress("route graphs timed; end-to-end leg")
     e2e = run_e2e(("idx", "gates", "counts", "offsets", "row_route", "route_row"))
     e2e_full = run_e2e(None)
 
@@ -448,7 +457,9 @@ def main_ours(args):
     strategies = {}
     if world == 1 and not args.quick:
         try:
+            _progress("strategy and expert-FFN records")
             strategies = bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak, peak_tf)
+            _progress("strategy records done")
         except Exception as exc:
             strategies = {"error": f"{type(exc).__name__}: {exc}"}
 
@@ -459,7 +470,9 @@ def main_ours(args):
     torch.cuda.empty_cache()
     if not args.quick:
         try:
+            _progress("expert-parallel parity check")
             ep_parity = check_ep_parity(torch, dist, dev, rank, world)
+            _progress("expert-parallel parity check done")
         except Exception as exc:
             ep_parity = {"ok": False, "error": f"{type(exc).__name__}: {exc}"}
         try:
@@ -480,7 +493,9 @@ def main_ours(args):
             ep["error"] = f"{type(exc).__name__}: {exc}"
 
     if rank == 0:
+        _progress("CPU baseline")
         cpu = run_cpu_reference(3, 1) if world == 1 else None
+        _progress("done")
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -587,7 +602,37 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
             ops.grouped_gemm(rows, w1, off, layout="nk", activation="gelu", out=hbuf)
             ops.grouped_gemm(hbuf, w2, off, layout="nk", out=ybuf)
 
-        us = event_us(ffn, n=10, warm=3)
+        # two FFNs per CUDA graph, 8 replays timed one by one: the launches cost no host time inside
+        # the timed region and the run stays short enough for burst clocks
+        def ffn_graph_us():
+            g_ffn, _ = capture(lambda i: ffn(), 2)
+            g_ffn.replay()
+            return med(timed(g_ffn, 8)) / 2 * 1e3
+
+        us = ffn_graph_us()
+        variants = None
+        if n_exp == 8:
+            # the same shape on the one-CTA kernel (two-tile units), same box, same protocol
+            from moe_routers_b200._lib import lib as _l
+            mode = _l.moe_set_gemm_mode(-1)
+            _l.moe_set_gemm_mode(mode & ~1)
+            variants = {"one_cta_kernel_us": ffn_graph_us()}
+            _l.moe_set_gemm_mode(mode & ~2)
+            variants["two_cta_one_issuer_us"] = ffn_graph_us()
+            _l.moe_set_gemm_mode(mode)
+            # context only: the library batched GEMM on the same operands, same protocol, without the
+            # activation (what the peak in MEASURED_PEAKS.json was measured with)
+            x3, h3 = rows.view(n_exp, -1, D), hbuf.view(n_exp, -1, HID)
+            y3 = ybuf.view(n_exp, -1, D)
+            w1t, w2t = w1.transpose(1, 2), w2.transpose(1, 2)
+
+            def ffn_lib():
+                torch.bmm(x3, w1t, out=h3)
+                torch.bmm(h3, w2t, out=y3)
+
+            g_lib, _ = capture(lambda i: ffn_lib(), 2)
+            g_lib.replay()
+            variants["library_bmm_no_activation_us"] = med(timed(g_lib, 8)) / 2 * 1e3
         wbytes = n_exp * 2 * D * HID * 2
         abytes = T * K_TOP * (D + 2 * HID + D) * 2
         t_tensor = flops / (peak_tf * 1e12) * 1e6
@@ -596,7 +641,10 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
             "t_us": us, "tflops": flops / (us * 1e-6) / 1e12, "flop": flops, "weight_bytes": wbytes,
             "bound": "tensor" if t_tensor >= t_hbm else "hbm (expert weights)",
             "frac_of_tensor_peak": flops / (us * 1e-6) / 1e12 / peak_tf,
-            "frac": max(t_tensor, t_hbm) / us, "floor_us": max(t_tensor, t_hbm), "peak_tflops": peak_tf}
+            "frac": max(t_tensor, t_hbm) / us, "floor_us": max(t_tensor, t_hbm), "peak_tflops": peak_tf,
+            "timing": "median of 8 replays of a CUDA graph holding 2 FFNs"}
+        if variants:
+            out[f"grouped_ffn_{n_exp}x{T * K_TOP // n_exp}"]["variants"] = variants
         if n_exp == 8:
             # configuration 3: masked_matmul, E=8: every expert runs densely over all T tokens
             w8 = (torch.randn(8, D, device=dev) / D ** 0.5).half()

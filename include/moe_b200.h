@@ -16,10 +16,12 @@
  *     its scratch, says what it shares);
  *   - environment switches, read once per process, all default to the fast
  *     path: MOE_B200_PDL=0 (no programmatic dependent launch between the
- *     route kernels; moe_set_pdl changes it at run time), MOE_B200_M64=0
- *     and MOE_B200_PAIR=0 (grouped GEMM: 128-row tiles only / single-tile
- *     work units), MOE_B200_GEMM_PRODUCERS=1 (grouped GEMM: one TMA-issuing
- *     warp), MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
+ *     route kernels; moe_set_pdl changes it at run time); grouped GEMM
+ *     variants, also changed at run time by moe_set_gemm_mode: MOE_B200_CTA2=0
+ *     (no two-CTA kernel), MOE_B200_CTA2_ISSUERS=1 (one MMA-issuing thread
+ *     in it), MOE_B200_PAIR=0 (single-tile work units), MOE_B200_M64=0
+ *     (128-row tiles only), MOE_B200_GEMM_PRODUCERS=1 (one TMA-issuing
+ *     warp); MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
  *
  * Each declaration names the piece of the reference (path:lines inside
  * santiweide/moe-routers) that it replaces.
@@ -82,6 +84,20 @@ long long moe_launch_count(void);
  * unless MOE_B200_PDL=0 is in the environment).  Process-wide; takes effect for launches issued
  * after the call.  Measurement helper; no counterpart in the reference. */
 int moe_set_pdl(int enabled);
+
+/* Variants the grouped GEMM may use; every combination computes the same result bits, the default
+ * (all on) is the fastest measured.  moe_set_gemm_mode(mode) replaces the set for launches issued
+ * after the call (process-wide) and returns the previous one; a negative mode only reads it.
+ * Measurement and test helper; no counterpart in the reference. */
+enum {
+  MOE_GEMM_TWO_CTA = 1,       /* two-CTA kernel (tcgen05 cta_group::2) for experts with >= 512 rows on average */
+  MOE_GEMM_TWO_ISSUERS = 2,   /* two MMA-issuing threads in the two-CTA kernel */
+  MOE_GEMM_TILE_PAIRS = 4,    /* one-CTA kernel: two 128-row tiles per work unit for such experts */
+  MOE_GEMM_M64 = 8,           /* one-CTA kernel: a last tile of <= 64 rows as UMMA M=64 */
+  MOE_GEMM_TWO_PRODUCERS = 16,/* one-CTA kernel: second TMA-issuing warp for single-tile units */
+  MOE_GEMM_ALL = 31
+};
+int moe_set_gemm_mode(int mode);
 
 /* Copy the status block's first word to the host.  THIS CALL SYNCHRONISES
  * `stream`.  0 means no kernel recorded an error; otherwise the value encodes

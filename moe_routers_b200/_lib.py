@@ -31,6 +31,7 @@ SIGNATURES = {
     "moe_set_wait_limit": (_i, [_p, _sz, C.c_ulonglong, _p]),
     "moe_launch_count": (C.c_longlong, []),
     "moe_set_pdl": (_i, [_i]),
+    "moe_set_gemm_mode": (_i, [_i]),
     "moe_topk_select": (_i, [_p, _i, _i, _i, _i, _p, _p, _p]),
     "moe_pack": (_i, [_p, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "moe_fused_select": (_i, [_p, _i, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),

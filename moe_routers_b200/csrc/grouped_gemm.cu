@@ -33,6 +33,7 @@
 // (plain 128-bit stores; no TMA and no multicast on peer memory).  The epilogue warp stages 32 rows
 // x 64 columns in shared memory and stores them as 128-byte row pieces, 4 rows per instruction,
 // so that a peer store is a full 128-byte write, not 32 scattered 16-byte ones.
+#include <atomic>
 #include <cstdlib>
 
 #include "sm100.cuh"
@@ -69,6 +70,7 @@ struct GParams {
   int m64;                  // 1: a last tile of <= 64 rows runs as UMMA M=64; 0: every tile is 128 rows
   int cta2_min_avg;         // two-CTA kernel when the experts hold at least this many rows on average (0: never)
   int stages_cta2;          // pipeline depth of the two-CTA kernel
+  int cta2_issuers;         // its MMA-issuing threads (1 or 2)
   int32_t* status;
 };
 
@@ -399,7 +401,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // 5-6 % faster (32 x 256 rows: 1228 -> 1163 us, 64 x 128: 1539 -> 1454 us); pair-mode units are not
     // issue-bound and measured 0-3 % slower with it, so they keep one.  Producer j owns the stages s
     // with s % producers == j and fills them in order (a stage's barrier parity is never ambiguous).
-    // MOE_B200_GEMM_PRODUCERS=1 in the environment keeps one issuing warp everywhere.
     const int pw = warp == 0 ? 0 : warp - 9;
     const int producers = pair ? 1 : min(p.producers, n_stages);
     if (lane == 0 && pw < producers) {
@@ -528,15 +529,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // The copies are ordinary TMA loads of this GPU's memory into the issuing CTA's own shared memory;
 // only their completion is signalled to the even CTA's barrier.  The even CTA's thread issues the
 // MMAs; its commits arrive on the barriers of both CTAs.
-// Warp roles (416 threads): warps 0, 10, 11, 12 issue the TMA copies (copies of one thread are served
-// one after another, so the operand boxes are spread over four), warp 1 owns TMEM and, in the even
-// CTA, issues the MMAs, warps 2..9 are the epilogue of the CTA's own 128 rows.
+// Warp roles (448 threads): warps 0, 10, 11, 12 issue the TMA copies (copies of one thread are served
+// one after another, so the operand boxes are spread over four), warp 1 owns TMEM, warps 1 and 13 of
+// the even CTA issue the MMAs, warps 2..9 are the epilogue of the CTA's own 128 rows.
 // An expert with an odd number of 128-row tiles ends with a unit of one tile, issued as a two-CTA
 // M=128 (64 rows per CTA, half the tensor time; the accumulator then holds each row's two column
 // halves on lanes l and l+64).  SwiGLU pairs a row's gate and up columns inside one lane, so there the
 // last unit stays M=256 with its second half past the expert's rows, computed and masked.  The
 // one-tile units are listed after all full ones, so the round-robin hands every cluster the same mix.
-constexpr int kCThreads = 416;
+constexpr int kCThreads = 448;
 // A stage holds two 64-wide k blocks of each operand (A block 0 | A block 1 | weight-half block 0 |
 // weight-half block 1, 16 KiB each): the commit that frees a stage costs the issuing thread about as
 // much as four MMAs, and with one k block per stage (six 32 KiB stages) the kernel measured 20 %
@@ -589,6 +590,7 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + (size_t)n_stages * kCStageBytes);
   // full[kMaxStages] (used in the even CTA), empty[kMaxStages], tmem_full[2], tmem_empty[2] (even CTA)
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);
+  uint32_t* s_seq = s_tmem + 1;                            // stages issued so far (two MMA-issuing threads)
   int32_t* s_mt = reinterpret_cast<int32_t*>(s_tmem + 4);  // [experts + 1] full units before each expert
   int32_t* s_mb = s_mt + p.experts + 1;                    // [experts + 1] one-tile units before each expert
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(
@@ -610,9 +612,10 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       mbar_init(empty0 + 8 * s, 1);  // one commit per use
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, 2 * kEpiThreads);  // every epilogue thread of both CTAs arrives
+      mbar_init(tfull0 + 8 * b, (uint32_t)p.cta2_issuers);  // one commit per MMA-issuing thread
+      mbar_init(tempty0 + 8 * b, 2 * kEpiThreads);          // every epilogue thread of both CTAs arrives
     }
+    *s_seq = 0;
     fence_barrier_init();
     fence_proxy_async();
     prefetch_tensormap(&tmap_a);
@@ -656,7 +659,7 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int total_units = (s_mt[p.experts] + s_mb[p.experts]) * p.n_tiles;
   const bool swiglu = p.act == MOE_ACT_SWIGLU;
 
-  if (warp == 0 || warp >= 10) {
+  if (warp == 0 || (warp >= 10 && warp <= 12)) {
     // ------------------------------ TMA producers ------------------------------
     // Producers 0/1 copy the two k blocks of this CTA's rows of A, producers 2/3 those of its half of
     // the weight tile.  Every producer waits for the stage to be free in its own CTA; the bytes of both CTAs complete on the
@@ -696,27 +699,50 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer (even CTA) ----------------------
-    if (lane == 0 && rank == 0) {
+  } else if (warp == 1 || warp == 13) {
+    // ------------------------------ MMA issuers (even CTA) ---------------------
+    // Issuing a stage's eight MMAs and the commit that frees the stage takes one thread about as long
+    // as the tensor pipe needs to run them, so two threads take the stages alternately: while one sits
+    // in its commit the other issues.  They issue strictly in stage order (`s_seq` counts the stages
+    // issued; warps 1 and 13 share a scheduler), so the accumulation order, and with it every result
+    // bit, is the same as with one thread.  Each thread commits its own MMAs: a stage's `empty`
+    // barrier by the thread that issued the stage, the unit's `tmem_full` barrier by both.
+    const int issuers = p.cta2_issuers;
+    const int me = warp == 1 ? 0 : 1;
+    if (lane == 0 && rank == 0 && me < issuers) {
       const uint32_t idesc256 = make_idesc_f16(2 * kBM, BN, p.bf16, 0, p.w_kn);
       const uint32_t idesc128 = make_idesc_f16(kBM, BN, p.bf16, 0, p.w_kn);
       const int total_a = s_mt[p.experts] * p.n_tiles;
+      volatile uint32_t* seq = s_seq;
       int s = 0;
       uint32_t ph = 0;
+      uint32_t g = 0;  // stages since the start of the kernel
       int local = 0;
       bool ok = true;
       for (int t = cluster; t < total_units && ok; t += n_clusters, ++local) {
         const uint32_t idesc = (t >= total_a && !swiglu) ? idesc128 : idesc256;
         const int ab = local & 1;  // units alternate between the two accumulators
         const uint32_t par = ((uint32_t)local >> 1) & 1u;
-        if (!mbar_wait(tempty0 + 8 * ab, par ^ 1u, p.status, 4)) break;
-        tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(full0 + 8 * s, ph, p.status, 2)) { ok = false; break; }
+        // The epilogue must have drained the accumulator before the unit's first MMA overwrites it.
+        // Both threads wait, also the one that issues later stages or none: its commit on `tmem_full`
+        // below must not fall into the barrier phase of the accumulator's previous unit.
+        if (!mbar_wait(tempty0 + 8 * ab, par ^ 1u, p.status, 4)) break;
+        for (int kb = 0; kb < kblocks; ++kb, ++g) {
+          const int s_now = s;
+          const uint32_t ph_now = ph;
+          if (++s == n_stages) { s = 0; ph ^= 1u; }
+          if (issuers == 2 && (int)(g & 1u) != me) continue;
+          if (!mbar_wait(full0 + 8 * s_now, ph_now, p.status, 2)) { ok = false; break; }
+          if (issuers == 2) {
+            // my turn: every earlier stage has been issued (bounded like every other wait)
+            bool turn = false;
+            for (int spin = 0; spin < (1 << 26); ++spin)
+              if (*seq == g) { turn = true; break; }
+            if (!turn) { record_error(p.status, kErrMbarTimeout | 5); ok = false; break; }
+          }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + (size_t)s * kCStageBytes);
+          const uint32_t a_addr = smem_u32(smem + (size_t)s_now * kCStageBytes);
           const uint32_t b_addr = a_addr + KH * kABytes;
 #pragma unroll
           for (int h = 0; h < KH; ++h) {
@@ -729,10 +755,13 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               umma_f16_pair(acc, adesc + 2 * k, bdesc, idesc, (uint32_t)((kb | h | k) != 0));
             }
           }
-          umma_commit_pair(empty0 + 8 * s, 3);  // the stage is free in both CTAs
-          if (++s == n_stages) { s = 0; ph ^= 1u; }
+          if (issuers == 2) {
+            tc_fence_before();
+            *seq = g + 1;  // the other thread may issue the next stage
+          }
+          umma_commit_pair(empty0 + 8 * s_now, 3);  // the stage is free in both CTAs
         }
-        umma_commit_pair(tfull0 + 8 * ab, 3);
+        if (ok) umma_commit_pair(tfull0 + 8 * ab, 3);  // (a thread without a stage in this unit arrives at once)
       }
     }
     __syncwarp();
@@ -772,6 +801,23 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
 namespace moe {
 namespace {
+// Which variants the grouped GEMM may use (MOE_GEMM_* bits).  Set from the environment at first use,
+// changed by moe_set_gemm_mode; every variant computes the same bits, the fastest set is the default.
+std::atomic<int> g_gemm_mode{-1};
+int gemm_mode() {
+  int m = g_gemm_mode.load(std::memory_order_relaxed);
+  if (m >= 0) return m;
+  auto off = [](const char* name) { const char* v = getenv(name); return v && v[0] == '0'; };
+  m = MOE_GEMM_ALL;
+  if (off("MOE_B200_CTA2")) m &= ~MOE_GEMM_TWO_CTA;
+  if (off("MOE_B200_PAIR")) m &= ~MOE_GEMM_TILE_PAIRS;
+  if (off("MOE_B200_M64")) m &= ~MOE_GEMM_M64;
+  { const char* v = getenv("MOE_B200_CTA2_ISSUERS"); if (v && v[0] == '1') m &= ~MOE_GEMM_TWO_ISSUERS; }
+  { const char* v = getenv("MOE_B200_GEMM_PRODUCERS"); if (v && v[0] == '1') m &= ~MOE_GEMM_TWO_PRODUCERS; }
+  g_gemm_mode.store(m, std::memory_order_relaxed);
+  return m;
+}
+
 int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_rows, const int32_t* offsets,
                         int experts, int rows, int K, int N, int w_layout, int64_t stride_w, int activation,
                         const float* row_scale, const void* bias, int dtype, int sm_margin, void* workspace,
@@ -809,20 +855,10 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
   p.row_scale = row_scale;
   p.c = static_cast<uint16_t*>(c);
   p.c_rows = reinterpret_cast<uint16_t* const*>(c_rows);
-  {
-    // MOE_B200_M64=0 in the environment keeps every tile at 128 rows (the default runs an expert's
-    // last tile as UMMA M=64 when it holds at most 64 rows: half the tensor time for that tile)
-    static const int m64 = [] { const char* v = getenv("MOE_B200_M64"); return (v && v[0] == '0') ? 0 : 1; }();
-    p.m64 = m64;
-  }
-  {
-    static const int producers = [] {
-      const char* v = getenv("MOE_B200_GEMM_PRODUCERS");
-      const int n = v ? atoi(v) : kProducerWarps;
-      return n < 1 ? 1 : (n > kProducerWarps ? kProducerWarps : n);
-    }();
-    p.producers = producers;
-  }
+  const int mode = gemm_mode();
+  // an expert's last tile runs as UMMA M=64 when it holds at most 64 rows: half the tensor time for it
+  p.m64 = (mode & MOE_GEMM_M64) ? 1 : 0;
+  p.producers = (mode & MOE_GEMM_TWO_PRODUCERS) ? kProducerWarps : 1;
   p.bias = static_cast<const uint16_t*>(bias);
   p.bf16 = dtype == MOE_BF16;
   p.status = static_cast<int32_t*>(workspace);
@@ -850,8 +886,8 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
   {
     // Pair mode (see the top of the file) pays when experts hold several full tiles: measured +10 %
     // at 8 x 1024 rows, +3 % at 8 x ~1030 and 16 x ~515, -7 % at 32 x ~260 rows (the epilogue of a
-    // pair is not hidden behind the next main loop).  MOE_B200_PAIR=0 in the environment disables it.
-    static const int pair_on = [] { const char* v = getenv("MOE_B200_PAIR"); return (v && v[0] == '0') ? 0 : 1; }();
+    // pair is not hidden behind the next main loop).
+    const int pair_on = (mode & MOE_GEMM_TILE_PAIRS) ? 1 : 0;
     int stages_pair = (227 * 1024 - fixed) / stage_pair;
     if (stages_pair > kMaxStages) stages_pair = kMaxStages;
     p.stages_pair = stages_pair;
@@ -864,11 +900,12 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
   if (sm_margin > 0 && sm_margin < sms) sms -= sm_margin;
   {
     // The two-CTA kernel takes the calls whose experts hold 512 rows or more on average (it replaces
-    // the two-tile units of one CTA there); MOE_B200_CTA2=0 in the environment disables it.
-    static const int cta2_on = [] { const char* v = getenv("MOE_B200_CTA2"); return (v && v[0] == '0') ? 0 : 1; }();
+    // the two-tile units of one CTA there).
+    const int cta2_on = (mode & MOE_GEMM_TWO_CTA) ? 1 : 0;
     int stages_cta2 = (227 * 1024 - fixed) / kCStageBytes;
     if (stages_cta2 > kMaxStages) stages_cta2 = kMaxStages;
     p.stages_cta2 = stages_cta2;
+    p.cta2_issuers = (mode & MOE_GEMM_TWO_ISSUERS) ? 2 : 1;
     p.cta2_min_avg = (cta2_on && p.bn == 256 && stages_cta2 >= 2 && sms >= 2) ? 4 * kBM : 0;
   }
   size_t stage_area = (size_t)stages * stage_single;
@@ -935,4 +972,10 @@ extern "C" int moe_grouped_gemm_rows(const void* a, const void* w, void* const* 
   if (!c_rows) return moe::fail(MOE_ERR_ARG, "moe_grouped_gemm_rows: null row table");
   return moe::grouped_gemm_launch(a, w, nullptr, c_rows, offsets, experts, rows, K, N, w_layout, stride_w, activation,
                                   row_scale, bias, dtype, sm_margin, workspace, workspace_bytes, stream);
+}
+
+extern "C" int moe_set_gemm_mode(int mode) {
+  const int before = moe::gemm_mode();
+  if (mode >= 0) moe::g_gemm_mode.store(mode & MOE_GEMM_ALL, std::memory_order_relaxed);
+  return before;
 }

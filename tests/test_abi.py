@@ -83,6 +83,11 @@ def test_argument_errors_do_not_launch(lib):
     assert L.moe_ipc_export(None, None, None) == 1 and "null" in lib.last_error()
     assert L.moe_set_wait_limit(None, 0, 1000, None) == 3
     assert L.moe_launch_count() >= 0 and L.moe_set_pdl(1) == 0
+    # grouped GEMM variants: the setter returns the previous set, a negative mode only reads
+    before = L.moe_set_gemm_mode(-1)
+    assert 0 <= before <= 31
+    assert L.moe_set_gemm_mode(5) == before and L.moe_set_gemm_mode(-1) == 5
+    assert L.moe_set_gemm_mode(before) == 5 and L.moe_set_gemm_mode(-1) == before
     # zero tokens is a valid no-op that needs no pointers
     assert L.moe_topk_select(None, lib.MOE_F16, 0, 64, 2, None, None, None) == 0
     assert L.moe_combine(None, lib.MOE_F16, None, None, 0, 8, 2, None, None) == 0

@@ -221,3 +221,39 @@ def test_grouped_gemm_scattered_rows_equal_dense(ops, N, act, dtype, bias, count
     unused = torch.ones(rows + 7, dtype=torch.bool)
     unused[perm] = False
     assert (got[unused].float() == 7.0).all()
+
+
+@pytest.mark.parametrize("counts,K,N,layout,act", [
+    ([1045, 1037, 1009, 1021, 994, 1050, 1012, 1024], 512, 1024, "nk", "gelu"),
+    ([600, 0, 257, 1230], 200, 512, "kn", None),
+    ([2048, 1, 1023], 256, 256, "nk", "swiglu"),
+])
+def test_grouped_gemm_variants_are_bit_identical(ops, counts, K, N, layout, act):
+    """Every kernel variant (two-CTA kernel with one or two MMA-issuing threads, two-tile units of one
+    CTA, single-tile units, M=64 last tiles on or off, one or two TMA warps) accumulates in the same
+    order, so the results must agree bit for bit, and a repeated call must reproduce itself."""
+    from moe_routers_b200._lib import lib
+
+    off = _segments(counts)
+    rows, e = int(off[-1]), len(counts)
+    g = torch.Generator().manual_seed(len(counts) + K)
+    a = torch.randn(rows, K, generator=g).half().cuda()
+    n_w = 2 * N if act == "swiglu" else N
+    shape = (e, n_w, K) if layout == "nk" else (e, K, n_w)
+    w = (torch.randn(*shape, generator=g) / K ** 0.5).half().cuda()
+    off_t = torch.from_numpy(off).cuda()
+    before = lib.moe_set_gemm_mode(-1)
+    try:
+        outs = {}
+        for mode in (31, 31, 29, 30, 4 | 8 | 16, 8 | 16, 16, 0):
+            lib.moe_set_gemm_mode(mode)
+            out = ops.grouped_gemm(a, w, off_t, layout=layout, activation=act)
+            torch.cuda.synchronize()
+            assert ops.read_status() == 0
+            outs.setdefault(mode, []).append(out.view(torch.int16).cpu())
+    finally:
+        lib.moe_set_gemm_mode(before)
+    ref = outs[31][0]
+    for mode, got in outs.items():
+        for o in got:
+            assert torch.equal(o, ref), f"mode {mode} differs"
