@@ -35,7 +35,7 @@ def case_ffn() -> None:
     x = torch.randn(8192, d, device="cuda").half()
     w1 = (torch.randn(8, h, d, device="cuda") / 64).half()
     off = torch.arange(0, 8193, 1024, device="cuda", dtype=torch.int32)
-    for _ in range(3):  # tensor-bound: 8 experts x 1024 rows (pair mode)
+    for _ in range(3):  # tensor-bound: 8 experts x 1024 rows (two-CTA kernel)
         ops.grouped_gemm(x, w1, off, layout="nk", activation="gelu")
     del w1
     w1b = (torch.randn(64, h, d, device="cuda") / 64).half()
