@@ -906,6 +906,9 @@ int grouped_gemm_launch(const void* a, const void* w, void* c, void* const* c_ro
     if (stages_cta2 > kMaxStages) stages_cta2 = kMaxStages;
     p.stages_cta2 = stages_cta2;
     p.cta2_issuers = (mode & MOE_GEMM_TWO_ISSUERS) ? 2 : 1;
+    // Below 512 rows per expert the odd last tiles weigh too much: a one-tile unit costs the two-CTA
+    // kernel almost a full unit's time (24 x 384 rows: 1390-1410 us against 1170-1180 on the one-CTA
+    // kernel; 32 x 256 rows, no odd tiles: 1060 against 1120).
     p.cta2_min_avg = (cta2_on && p.bn == 256 && stages_cta2 >= 2 && sms >= 2) ? 4 * kBM : 0;
   }
   size_t stage_area = (size_t)stages * stage_single;

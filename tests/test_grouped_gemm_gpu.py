@@ -198,7 +198,7 @@ def test_demo_pipeline_on_device(ops):
 def test_grouped_gemm_scattered_rows_equal_dense(ops, N, act, dtype, bias, counts):
     """`out_rows`: every result row stored at its own address.  With the addresses of a permuted
     buffer the result must be the dense result, row-permuted, bit for bit (same kernel arithmetic);
-    rows that no address points to stay untouched.  (The second set of counts runs in pair mode
+    rows that no address points to stay untouched.  (The second set of counts runs on the two-CTA kernel
     where the tile has 256 accumulator columns.)"""
     K = 192
     off = _segments(counts)
