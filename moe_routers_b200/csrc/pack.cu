@@ -201,8 +201,9 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
   const uint32_t buf0 = (uint32_t)__cvta_generic_to_shared(s_buf);
   const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(s_bar);
   // item m of this thread is tile item (warp + m*8); it lives in buffer (warp + (m % depth)*8)
+  // (rows of at most one chunk, the usual case, need no division)
   auto item_src = [&](int it, uint32_t& bytes) -> const char* {
-    const int row = it / chunks, ch = it % chunks;
+    const int row = chunks == 1 ? it : it / chunks, ch = chunks == 1 ? 0 : it % chunks;
     const size_t ofs = (size_t)ch * chunk_bytes;
     bytes = (uint32_t)min((size_t)chunk_bytes, row_bytes - ofs);
     return x + (size_t)(t0 + row) * row_bytes + ofs;
@@ -226,13 +227,16 @@ pack_scatter_bulk_kernel(const char* __restrict__ x, const int32_t* __restrict__
 
   if (lane == 0) {
     bool ok = true;
+    int slot = 0;        // m % depth and the parity of m / depth, advanced without divisions
+    uint32_t par = 0;
     for (int m = 0; ok; ++m) {
       const int it = warp + m * kBulkIssuers;
       if (it >= items) break;
-      const int b = warp + (m % depth) * kBulkIssuers;
-      ok = sm100::mbar_wait(bar0 + 8u * b, (uint32_t)(m / depth) & 1u, status, 8);
+      const int b = warp + slot * kBulkIssuers;
+      ok = sm100::mbar_wait(bar0 + 8u * b, par, status, 8);
       if (!ok) break;
-      const int row = it / chunks, ch = it % chunks;
+      if (++slot == depth) { slot = 0; par ^= 1u; }
+      const int row = chunks == 1 ? it : it / chunks, ch = chunks == 1 ? 0 : it % chunks;
       uint32_t bytes;
       (void)item_src(it, bytes);
       for (int j = 0; j < top_k; ++j) {

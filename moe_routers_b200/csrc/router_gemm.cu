@@ -283,8 +283,11 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int block = blockIdx.x;
   const int krank = (int)cluster_ctarank();
   const int S = p.splitk;
-  const int kb0 = (int)(((long long)p.kblocks * krank) / S);
-  const int kb1 = (int)(((long long)p.kblocks * (krank + 1)) / S);
+  // this CTA's k blocks: kblocks * krank / S with S = 1, 2 or 4 (shifts: the prologue is on the
+  // critical path of the first copy)
+  const int sh = S == 4 ? 2 : (S == 2 ? 1 : 0);
+  const int kb0 = (int)(((unsigned)p.kblocks * (unsigned)krank) >> sh);
+  const int kb1 = (int)(((unsigned)p.kblocks * (unsigned)(krank + 1)) >> sh);
   const int nkb = kb1 - kb0;
 
   const uint32_t full0 = smem_u32(s_bar);
@@ -323,15 +326,21 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // still running: everything above overlaps it; global memory is first touched after this wait.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (lane == 0 && warp < producers) {
+      // stage, its owner and the parity of its use advance without divisions: this thread is on the
+      // critical path of its fills
+      int s = 0, owner = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < nkb; ++it) {
-        const int s = it % p.stages;
-        if (s % producers != warp) continue;
-        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1)) break;
-        mbar_expect_tx(full0 + 8 * s, (uint32_t)(kABytes + b_bytes));
+        const int s_now = s, owner_now = owner;
+        const uint32_t ph_now = ph;
+        if (++owner == producers) owner = 0;
+        if (++s == p.stages) { s = 0; owner = 0; ph ^= 1u; }
+        if (owner_now != warp) continue;
+        if (!mbar_wait(empty0 + 8 * s_now, ph_now ^ 1u, p.status, 1)) break;
+        mbar_expect_tx(full0 + 8 * s_now, (uint32_t)(kABytes + b_bytes));
         const int kb = kb0 + it;
-        tma_load_2d(smem_u32(sA + (size_t)s * kABytes), &tmap_x, full0 + 8 * s, kb * kBlockK, block * kBlockTokens);
-        tma_load_2d(smem_u32(sB + (size_t)s * b_bytes), &tmap_w, full0 + 8 * s, kb * kBlockK, 0);
+        tma_load_2d(smem_u32(sA + (size_t)s_now * kABytes), &tmap_x, full0 + 8 * s_now, kb * kBlockK, block * kBlockTokens);
+        tma_load_2d(smem_u32(sB + (size_t)s_now * b_bytes), &tmap_w, full0 + 8 * s_now, kb * kBlockK, 0);
       }
     }
     __syncwarp();
@@ -353,10 +362,14 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (lane == 0 && m < p.nacc) {
       const uint32_t idesc = make_idesc_f16(kBlockTokens, E, p.bf16, 0, 0);
       bool fresh = true;  // accumulator m holds nothing yet
+      int s_next = 0, owner = 0;
+      uint32_t ph_next = 0;
       for (int it = 0; it < nkb; ++it) {
-        const int s = it % p.stages;
-        if (s % p.nacc != m) continue;
-        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+        const int s = s_next, owner_now = owner;
+        const uint32_t ph = ph_next;
+        if (++owner == p.nacc) owner = 0;
+        if (++s_next == p.stages) { s_next = 0; owner = 0; ph_next ^= 1u; }
+        if (owner_now != m) continue;
         if (!mbar_wait(full0 + 8 * s, ph, p.status, 2)) break;
         tc_fence_after();
         const uint64_t adesc = make_desc_kmajor_sw128(smem_u32(sA + (size_t)s * kABytes));
