@@ -136,8 +136,10 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     }
   }
 }
-__device__ __forceinline__ void cluster_arrive_release() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+// Start-of-kernel arrival: the barrier initialisations were released to the cluster by
+// fence.mbarrier_init, nothing else has to be visible to the other CTAs yet.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -295,23 +297,26 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t tmem_full = smem_u32(s_bar + 2 * kMaxStages);
   const uint32_t part_full = smem_u32(s_bar + 2 * kMaxStages + 1);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, 1);
-    }
-    mbar_init(tmem_full, (uint32_t)p.nacc);  // one commit per issuing warp
-    mbar_init(part_full, kEpiThreads);       // S source CTAs x (4 / S) warps x 32 lanes
-    fence_barrier_init();
-    fence_proxy_async();
+  // One barrier per thread (the prologue is on the critical path of the first copy); the descriptor
+  // fetches start at once, from a warp that initialises nothing.
+  if (threadIdx.x == kThreads - 32) {
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_w);
+  }
+  if ((int)threadIdx.x < 2 * p.stages + 2) {
+    const int t = (int)threadIdx.x;
+    if (t < p.stages) mbar_init(full0 + 8 * t, 1);
+    else if (t < 2 * p.stages) mbar_init(empty0 + 8 * (t - p.stages), 1);
+    else if (t == 2 * p.stages) mbar_init(tmem_full, (uint32_t)p.nacc);  // one commit per issuing warp
+    else mbar_init(part_full, kEpiThreads);  // S source CTAs x (4 / S) warps x 32 lanes
+    fence_barrier_init();
+    fence_proxy_async();
   }
   for (int i = threadIdx.x; i < 4 * E; i += kThreads) s_hist[i] = 0;
   __syncthreads();
   // Remote shared-memory traffic below needs every CTA of the cluster to be running with its
   // barriers initialised: arrive now, wait just before the first remote access.
-  cluster_arrive_release();
+  cluster_arrive_relaxed();
   // Let a dependent kernel (launched with programmatic stream serialisation) start its own input
   // prefetch as soon as it finds room; it still waits for this grid to finish before reading what
   // we write.
