@@ -265,6 +265,7 @@ def main_ours(args):
     def capture(fn, n):
         """K calls of fn in one CUDA graph; returns (graph, kernel launches captured)."""
         stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())  # inputs may still be in flight on the caller's stream
         with torch.cuda.stream(stream):
             fn(0)
             torch.cuda.synchronize()
@@ -580,6 +581,7 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
                                   "bound": "sync latency (589,824 compulsory bytes)", "algorithmic_bytes": byt,
                                   "frac": byt / (us * 1e-6) / 1e9 / peak,
                                   "reference_traffic_model_bytes": (2 + 4 * 10) * 2 * T * E * 4}
+    _progress("  naive_topk and sinkhorn routes timed")
     # combine
     o = ops.route_fused(xs[0], w, K_TOP)
     ys = [o["packed"]] + [o["packed"].clone() for _ in range(3)]  # 4 x 67 MB of expert outputs > L2
@@ -589,6 +591,7 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
     del ys
     # grouped expert FFN 4096 -> 8192 -> 4096 on 8192 routed rows: 8 experts x 1024 rows (tensor-bound),
     # 64 experts x 128 rows (weight-bound)
+    _progress("  combine timed")
     flops = 2.0 * T * K_TOP * (D * HID + HID * D)
     rows = torch.randn(T * K_TOP, D, device=dev).half()
     for n_exp in (8, 64):
@@ -610,6 +613,7 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
             return med(timed(g_ffn, 8)) / 2 * 1e3
 
         us = ffn_graph_us()
+        _progress(f"  grouped FFN {n_exp} experts timed")
         variants = None
         if n_exp == 8:
             # the same shape on the one-CTA kernel (two-tile units), same box, same protocol
@@ -653,7 +657,9 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
                 r = st.route("masked_matmul", xs[0], w8, K_TOP)
                 st.masked_matmul_forward(xs[0], r, w1, w2, K_TOP)
 
+            _progress("  FFN variants timed")
             us = event_us(mm, n=5, warm=2)
+            _progress("  masked_matmul timed")
             mflops = 8.0 * T * 2 * (D * HID + HID * D) + 2.0 * T * D * 8
             out["masked_matmul_E8"] = {"t_layer_us": us, "tokens_per_s": T / (us * 1e-6), "bound": "tensor", "flop": mflops,
                                        "tflops": mflops / (us * 1e-6) / 1e12,
@@ -662,6 +668,7 @@ def bench_strategies(torch, ops, dev, xs, w, capture, timed, med, event_us, peak
         torch.cuda.empty_cache()
     # CPU figures beside the strategies the reference has a CPU path for (bench_router.py:484-505)
     for name, strat in (("naive_topk_plain", "naive_topk"), ("sinkhorn_plain", "sinkhorn")):
+        _progress(f"  CPU reference, {strat}")
         c = run_cpu_reference(2, 1, strategy=strat, skew=False)
         out[name]["cpu_baseline"] = {"value": c["value"], "unit": "tokens/s", "cores": c["cores"], "kind": c["kind"],
                                      "sample": "2 full passes of T=4096 tokens", "breakdown_ms": c["breakdown_ms"]}

@@ -80,6 +80,14 @@ constexpr int kStageWarpBytes = 32 * kStageRowBytes;
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
 
+// An expert's segment [seg_lo, seg_hi) of the row buffer, whatever the offsets array holds: both ends
+// are forced into [0, rows] and hi >= lo, so offsets that are not (yet) valid - read before the
+// kernel that writes them has run, say - cost at most rows/128 + experts tiles and never address a
+// row outside the buffer.
+__device__ __forceinline__ int seg_lo(const GParams& p, int e) { return max(0, min(p.offsets[e], p.rows)); }
+__device__ __forceinline__ int seg_hi(const GParams& p, int e) { return max(seg_lo(p, e), min(p.offsets[e + 1], p.rows)); }
+__device__ __forceinline__ int routed_rows(const GParams& p) { return max(0, min(p.offsets[p.experts], p.rows)); }
+
 // Whether this call runs on the two-CTA kernel: decided on the device from the number of rows
 // actually routed (the host only knows the capacity of the row buffer); both kernels of a call
 // evaluate it and exactly one of them does the work.
@@ -105,23 +113,23 @@ __device__ __forceinline__ int last_not_above(const int32_t* pre, int n, int n_t
   }
   return lo;
 }
-__device__ __forceinline__ Unit decode_unit(const int32_t* s_a, const int32_t* s_b, const int32_t* offsets, int experts,
-                                            int rows, int n_tiles, int pair, int t) {
+__device__ __forceinline__ Unit decode_unit(const int32_t* s_a, const int32_t* s_b, const GParams& p, int pair, int t) {
   Unit u;
+  const int experts = p.experts, n_tiles = p.n_tiles;
   const int total_a = s_a[experts] * n_tiles;
   if (t < total_a) {
     u.e = last_not_above(s_a, experts, n_tiles, t);
     const int per = s_a[u.e + 1] - s_a[u.e];
     const int local = t - s_a[u.e] * n_tiles;
     u.nt = local / per;
-    u.row0 = offsets[u.e] + (local % per) * (pair ? 2 * kBM : kBM);
+    u.row0 = seg_lo(p, u.e) + (local % per) * (pair ? 2 * kBM : kBM);
     u.two = pair != 0;
   } else {
     const int tb = t - total_a;
     u.e = last_not_above(s_b, experts, n_tiles, tb);
     u.nt = tb - s_b[u.e] * n_tiles;
-    const int cnt = min(offsets[u.e + 1], rows) - offsets[u.e];
-    u.row0 = offsets[u.e] + ((cnt + kBM - 1) / kBM - 1) * kBM;  // the expert's last tile
+    const int lo = seg_lo(p, u.e), cnt = seg_hi(p, u.e) - lo;
+    u.row0 = lo + ((cnt + kBM - 1) / kBM - 1) * kBM;  // the expert's last tile
     u.two = false;
   }
   return u;
@@ -318,7 +326,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int b_bytes = BN * kBK * 2;
   // Pair mode is chosen here, from the number of rows actually routed (the host only knows the
   // capacity of the row buffer): every thread reads the same total and takes the same branch.
-  const int routed = min(p.offsets[p.experts], p.rows);
+  const int routed = routed_rows(p);
   if (cta2_mode(p, routed)) return;  // grouped_gemm_cta2_kernel, launched next, does this call's work
   const int pair = (p.pair_min_avg > 0 && (long long)routed >= (long long)p.pair_min_avg * p.experts) ? 1 : 0;
   const int n_stages = pair ? p.stages_pair : p.stages;
@@ -369,7 +377,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int e = eb + lane;
       int ca = 0, cb = 0;
       if (e < p.experts) {
-        const int lo = p.offsets[e], hi = min(p.offsets[e + 1], p.rows);
+        const int lo = seg_lo(p, e), hi = seg_hi(p, e);
         const int tiles = hi > lo ? (hi - lo + kBM - 1) / kBM : 0;
         ca = pair ? tiles / 2 : tiles;
         cb = pair ? tiles & 1 : 0;
@@ -408,7 +416,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t ph = 0;  // on the critical path of its stages)
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.rows, p.n_tiles, pair, t);
+        const Unit u = decode_unit(s_mt, s_mb, p, pair, t);
         const int e = u.e, nt = u.nt, row0 = u.row0;
         const bool two = u.two;  // the unit has a second tile
         for (int kb = 0; kb < p.kblocks; ++kb) {
@@ -438,8 +446,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int local = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-        const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.rows, p.n_tiles, pair, t);
-        const int seg_end = min(p.offsets[u.e + 1], p.rows);
+        const Unit u = decode_unit(s_mt, s_mb, p, pair, t);
+        const int seg_end = seg_hi(p, u.e);
         const int row0 = u.row0;
         const bool two = u.two;
         // a last tile that holds at most 64 rows of its expert costs half the tensor time as M=64
@@ -489,9 +497,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-      const Unit u = decode_unit(s_mt, s_mb, p.offsets, p.experts, p.rows, p.n_tiles, pair, t);
+      const Unit u = decode_unit(s_mt, s_mb, p, pair, t);
       const int e = u.e, nt = u.nt;
-      const int seg_end = min(p.offsets[e + 1], p.rows);
+      const int seg_end = seg_hi(p, e);
       for (int h = 0; h < PM; ++h) {
         const int ab = pair ? h : (local & 1);
         const uint32_t par = pair ? ((uint32_t)local & 1u) : (((uint32_t)local >> 1) & 1u);
@@ -561,13 +569,13 @@ __device__ __forceinline__ CUnit decode_cta2(const int32_t* s_a, const int32_t* 
     const int per = s_a[u.e + 1] - s_a[u.e];
     const int local = t - s_a[u.e] * p.n_tiles;
     u.nt = local / per;
-    u.row0 = p.offsets[u.e] + (local % per) * kCRows;
+    u.row0 = seg_lo(p, u.e) + (local % per) * kCRows;
     u.one = false;
   } else {
     const int tb = t - total_a;
     u.e = last_not_above(s_b, p.experts, p.n_tiles, tb);
     u.nt = tb - s_b[u.e] * p.n_tiles;
-    u.row0 = p.offsets[u.e] + (s_a[u.e + 1] - s_a[u.e]) * kCRows;  // after the expert's full units
+    u.row0 = seg_lo(p, u.e) + (s_a[u.e + 1] - s_a[u.e]) * kCRows;  // after the expert's full units
     u.one = true;
   }
   return u;
@@ -578,7 +586,7 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                          const __grid_constant__ CUtensorMap tmap_w, const GParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   // every CTA reads the same total and takes the same branch (no barrier has been touched yet)
-  if (!cta2_mode(p, min(p.offsets[p.experts], p.rows))) return;
+  if (!cta2_mode(p, routed_rows(p))) return;
   if ((smem_u32(smem) & 1023u) != 0u) {  // the same in both CTAs of a pair
     record_error(p.status, kErrBadIndex | 0xfd);
     return;
@@ -633,7 +641,7 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int e = eb + lane;
       int ca = 0, cb = 0;
       if (e < p.experts) {
-        const int lo = p.offsets[e], hi = min(p.offsets[e + 1], p.rows);
+        const int lo = seg_lo(p, e), hi = seg_hi(p, e);
         const int tiles = hi > lo ? (hi - lo + kBM - 1) / kBM : 0;
         ca = tiles / 2;
         cb = tiles & 1;
@@ -772,7 +780,7 @@ grouped_gemm_cta2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int local = 0;
     for (int t = cluster; t < total_units; t += n_clusters, ++local) {
       const CUnit u = decode_cta2(s_mt, s_mb, p, t);
-      const int seg_end = min(p.offsets[u.e + 1], p.rows);
+      const int seg_end = seg_hi(p, u.e);
       const int ab = local & 1;
       if (!mbar_wait(tfull0 + 8 * ab, ((uint32_t)local >> 1) & 1u, p.status, 3)) break;
       tc_fence_after();

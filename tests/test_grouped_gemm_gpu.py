@@ -257,3 +257,34 @@ def test_grouped_gemm_variants_are_bit_identical(ops, counts, K, N, layout, act)
     for mode, got in outs.items():
         for o in got:
             assert torch.equal(o, ref), f"mode {mode} differs"
+
+
+@pytest.mark.parametrize("offsets", [
+    [-5000, 300_000_000, -(2 ** 31), 17, 9],      # negative, far past the buffer, decreasing
+    [2 ** 31 - 1] * 5,
+    [0, 700, 650, 2 ** 30, 1400],
+])
+@pytest.mark.parametrize("N", [256, 64])
+def test_grouped_gemm_tolerates_invalid_offsets(ops, offsets, N):
+    """The offsets come from another kernel; a caller that launches the GEMM on a stream that does not
+    wait for that kernel hands it whatever the memory held.  Segments are forced into [0, rows] inside
+    the kernels, so such a call stays short (at most rows/128 + experts tiles), records no error and
+    writes only rows of the result buffer."""
+    import time
+
+    rows, K, e = (2400 if N == 256 else 1400), 128, 4  # 2400 rows: the two-CTA kernel where the total allows
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(rows, K, generator=g).half().cuda()
+    w = (torch.randn(e, N, K, generator=g) / K ** 0.5).half().cuda()
+    off = torch.tensor(offsets, dtype=torch.int64).to(torch.int32).cuda()
+    guard = torch.full((rows + 256, N), 7.0, dtype=torch.float16, device="cuda")
+    out = guard[128:128 + rows]  # the result buffer sits between two guard bands
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ops.grouped_gemm(a, w, off, layout="nk", out=out)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0
+    assert ops.read_status() == 0
+    assert (guard[:128].float() == 7.0).all() and (guard[128 + rows:].float() == 7.0).all()
+    # rows inside clamped segments hold finite GEMM results, the others are untouched
+    assert torch.isfinite(out.float()).all()
