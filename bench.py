@@ -410,7 +410,9 @@ def main_ours(args):
     # results.  `latency_ms` is one step alone (upload, kernels, download in series).
     from moe_routers_b200.host import HostRouter
 
-    x_host = xs[0].cpu().pin_memory()
+    from moe_routers_b200.host import pin_near
+
+    x_host = pin_near(xs[0].cpu(), dev)  # the caller's batch, pinned on the GPU's NUMA node
 
     def run_e2e(download):
         hr = HostRouter(T, D, w_cpu, K_TOP, depth=2, skew_experts=SKEW_N, skew_bias=SKEW_B, device=dev,

@@ -339,6 +339,11 @@ int moe_ipc_close(void* base);
  * moe_ipc_open and adds the offset.  The allocation must come from cudaMalloc. */
 int moe_ipc_export(const void* ptr, void* handle64_out, size_t* offset_out);
 
+/* PCI address of CUDA device `device` as "domain:bus:device.function" (cudaDeviceGetPCIBusId) into
+ * the host buffer `out` of `len` bytes (>= 16).  Host-side helper: HostRouter uses it to place its
+ * pinned staging buffers on the NUMA node the GPU is attached to.  No counterpart in the reference. */
+int moe_device_pci_bus_id(int device, char* out, int len);
+
 int moe_ep_push(const void* local, void* const* peer_bufs, const int32_t* counts_all, int experts, int world,
                 int rank, int combine, int d, int elem_bytes, int32_t* local_offsets, void* stream);
 

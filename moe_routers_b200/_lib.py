@@ -45,6 +45,7 @@ SIGNATURES = {
     "moe_ipc_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "moe_ipc_close": (_i, [_p]),
     "moe_ipc_export": (_i, [_p, C.c_char_p, C.POINTER(C.c_size_t)]),
+    "moe_device_pci_bus_id": (_i, [_i, C.c_char_p, _i]),
     "moe_ep_push": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]),
     "moe_ep_signal": (_i, [_p, _i, _i, _i, _i, _p, _p, _sz, _i, _p]),
     "moe_ep_wait": (_i, [_p, _i, _i, _i, _p, _sz, _p]),

@@ -109,3 +109,10 @@ extern "C" int moe_read_status(const void* workspace, void* stream, int* status_
   }
   return MOE_OK;
 }
+
+extern "C" int moe_device_pci_bus_id(int device, char* out, int len) {
+  if (out == nullptr || len < 16) return moe::fail(MOE_ERR_ARG, "moe_device_pci_bus_id: buffer of at least 16 bytes needed");
+  const cudaError_t e = cudaDeviceGetPCIBusId(out, len, device);
+  if (e != cudaSuccess) return moe::fail(MOE_ERR_DEVICE, "moe_device_pci_bus_id: %s", cudaGetErrorString(e));
+  return MOE_OK;
+}

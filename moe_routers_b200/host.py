@@ -3,7 +3,8 @@
 The reference's operator takes device tensors (kernels/fused_select.cu:203-215); a caller that
 keeps activations on the host pays one upload of `x` and one download of the five results per
 call.  `HostRouter` keeps `depth` slots, each with its own stream, device buffers and pinned host
-result buffers, so that the download of batch i (device -> host copy engine) runs while batch
+result buffers (allocated on the NUMA node the GPU is attached to; `pin_near` does the same for a
+caller's input batches), so that the download of batch i (device -> host copy engine) runs while batch
 i+1 uploads (host -> device copy engine) and routes:
 
     r = HostRouter(tokens, d_model, w_router_host, top_k=2)
@@ -15,9 +16,71 @@ All compute is the library's route kernels; nothing here falls back to the CPU.
 """
 from __future__ import annotations
 
+import contextlib
+import ctypes
+import os
+
 import torch
 
 from . import ops
+
+
+def parse_cpulist(text: str) -> set:
+    """CPU numbers of a sysfs cpulist ("0-31,64-95")."""
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def local_cpus(device, sysfs: str = "/sys") -> set:
+    """CPUs of the NUMA node that CUDA device `device` is attached to; empty when the platform does
+    not say (no sysfs entry, node -1) - the caller then leaves the thread where it is."""
+    from ._lib import lib
+
+    try:
+        buf = ctypes.create_string_buffer(32)
+        if lib.moe_device_pci_bus_id(int(torch.device(device).index or 0), buf, 32) != 0:
+            return set()
+        bdf = buf.value.decode().lower()
+        with open(os.path.join(sysfs, "bus/pci/devices", bdf, "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return set()
+        with open(os.path.join(sysfs, "devices/system/node", f"node{node}", "cpulist")) as f:
+            return parse_cpulist(f.read())
+    except (OSError, ValueError):
+        return set()
+
+
+@contextlib.contextmanager
+def numa_local(device, cpus=None):
+    """Run the body on CPUs next to the GPU, so that host memory pinned inside it lands on the GPU's
+    own NUMA node (first touch): with one rank per GPU on a two-socket host, staging buffers on the
+    far socket share the inter-socket link with every other rank's copies.  No-op where the CPUs are
+    unknown or not in the thread's allowed set."""
+    before = None
+    try:
+        want = (local_cpus(device) if cpus is None else set(cpus)) & os.sched_getaffinity(0)
+        if want:
+            before = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, want)
+    except (OSError, AttributeError):
+        before = None
+    try:
+        yield
+    finally:
+        if before is not None:
+            os.sched_setaffinity(0, before)
+
+
+def pin_near(t: torch.Tensor, device) -> torch.Tensor:
+    """A pinned host copy of `t` allocated on the NUMA node of `device`."""
+    with numa_local(device):
+        return t.contiguous().pin_memory()
 
 
 class HostRouter:
@@ -37,7 +100,7 @@ class HostRouter:
         self.tokens, self.d, self.k = int(tokens), int(d_model), int(top_k)
         self.skew = (int(skew_experts), float(skew_bias))
         self.upload_w = bool(upload_weight_each_call)
-        self.w_host = w_router if w_router.is_pinned() else w_router.contiguous().pin_memory()
+        self.w_host = w_router if w_router.is_pinned() else pin_near(w_router, self.device)
         self.slots = []
         for _ in range(depth):
             s = torch.cuda.Stream(device=self.device)
@@ -50,7 +113,8 @@ class HostRouter:
             unknown = [n for n in names if n not in dev_out or n == "workspace"]
             if unknown:
                 raise ValueError(f"unknown route outputs: {unknown}")
-            host_out = {n: torch.empty(dev_out[n].shape, dtype=dev_out[n].dtype).pin_memory() for n in names}
+            with numa_local(self.device):  # pinned result buffers next to the GPU
+                host_out = {n: torch.empty(dev_out[n].shape, dtype=dev_out[n].dtype).pin_memory() for n in names}
             self.slots.append(dict(stream=s, x=x_dev, w=w_dev, dev=dev_out, host=host_out,
                                    done=torch.cuda.Event(), busy=False))
         torch.cuda.synchronize(self.device)

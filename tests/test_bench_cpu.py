@@ -42,3 +42,42 @@ def test_non_zero_ranks_of_the_reference_arm_stay_silent():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_numa_helpers_parse_sysfs(tmp_path, monkeypatch):
+    """The helpers that place pinned staging buffers next to the GPU: cpulist parsing, the sysfs walk
+    with a fake tree and a fake PCI address, and the affinity context manager leaving the thread's
+    affinity as it found it."""
+    import os
+
+    from moe_routers_b200 import host
+
+    assert host.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert host.parse_cpulist("") == set()
+
+    class FakeLib:
+        def moe_device_pci_bus_id(self, device, buf, n):
+            buf.value = b"0000:1B:00.0"
+            return 0
+
+    import moe_routers_b200._lib as _lib
+
+    monkeypatch.setattr(_lib, "lib", FakeLib())
+    dev_dir = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev_dir.mkdir(parents=True)
+    (dev_dir / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("4-7\n")
+    assert host.local_cpus("cuda:0", sysfs=str(tmp_path)) == {4, 5, 6, 7}
+    (dev_dir / "numa_node").write_text("-1\n")
+    assert host.local_cpus("cuda:0", sysfs=str(tmp_path)) == set()
+    assert host.local_cpus("cuda:0", sysfs=str(tmp_path / "missing")) == set()
+
+    before = os.sched_getaffinity(0)
+    one = {sorted(before)[0]}
+    with host.numa_local("cuda:0", cpus=one):
+        assert os.sched_getaffinity(0) == one
+    assert os.sched_getaffinity(0) == before
+    with host.numa_local("cuda:0", cpus={10 ** 6}):  # not in the allowed set: nothing changes
+        assert os.sched_getaffinity(0) == before
