@@ -288,3 +288,21 @@ def test_grouped_gemm_tolerates_invalid_offsets(ops, offsets, N):
     assert (guard[:128].float() == 7.0).all() and (guard[128 + rows:].float() == 7.0).all()
     # rows inside clamped segments hold finite GEMM results, the others are untouched
     assert torch.isfinite(out.float()).all()
+
+
+def test_grouped_gemm_sm_margin_same_result(ops):
+    """`sm_margin` leaves SMs free for a concurrent communication kernel: fewer persistent CTAs (or
+    CTA pairs) walk the same unit list, so the result must not change.  Shape on the two-CTA kernel."""
+    counts = [1100, 513, 0, 1200]
+    off = _segments(counts)
+    rows, e, K, N = int(off[-1]), len(counts), 256, 512
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(rows, K, generator=g).half().cuda()
+    w = (torch.randn(e, N, K, generator=g) / K ** 0.5).half().cuda()
+    off_t = torch.from_numpy(off).cuda()
+    ref = ops.grouped_gemm(a, w, off_t, layout="nk", activation="gelu")
+    for margin in (1, 21, 140, 147):
+        got = ops.grouped_gemm(a, w, off_t, layout="nk", activation="gelu", sm_margin=margin)
+        torch.cuda.synchronize()
+        assert ops.read_status() == 0
+        assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), margin
