@@ -21,7 +21,9 @@
  *     (no two-CTA kernel), MOE_B200_CTA2_ISSUERS=1 (one MMA-issuing thread
  *     in it), MOE_B200_PAIR=0 (single-tile work units), MOE_B200_M64=0
  *     (128-row tiles only), MOE_B200_GEMM_PRODUCERS=1 (one TMA-issuing
- *     warp); MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
+ *     warp); MOE_B200_ROUTER_BULK=0 (router kernel: split-K partials exchanged
+ *     with remote stores also where a bulk copy would do);
+ *     MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
  *
  * Each declaration names the piece of the reference (path:lines inside
  * santiweide/moe-routers) that it replaces.

@@ -57,6 +57,7 @@ struct RouterParams {
   int epad;  // experts rounded up to the UMMA N granule (16); padded logit columns are never selected
   int kblocks, splitk, stages, tmem_cols, num_tiles;
   int stage_in_ring;  // the exchange's transpose tiles reuse the pipeline stages
+  int bulk_push;      // the exchange moves a warp's 32 x (E + 4) quarter with one bulk copy (E == 64 only)
   int nacc;  // MMA-issuing warps = TMEM accumulators (1 or 2; at most the stage count)
   // bit (2 * k-slice rank + m): issuing warp m gets at least one k-block of that k slice, i.e.
   // accumulator m holds a partial sum (the other was never written)
@@ -135,6 +136,15 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
       return false;
     }
   }
+}
+// Shared memory of this CTA -> shared memory of a CTA of the cluster, completion counted in bytes on an
+// mbarrier of the destination CTA (both given as shared::cluster addresses); 16-byte granularity.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                     uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster),
+               "r"(src_cta), "r"(bytes), "r"(bar_cluster)
+               : "memory");
 }
 // Start-of-kernel arrival: the barrier initialisations were released to the cluster by
 // fence.mbarrier_init, nothing else has to be visible to the other CTAs yet.
@@ -236,6 +246,11 @@ __device__ __forceinline__ void select_phase(const RouterParams& p, const float*
                                              uint32_t part_full, int st, int block, int krank) {
   const int S = p.splitk;
   const bool arrived = mbar_wait_cluster(part_full, 0, p.status, 4);
+  // bulk exchange: every copy into this CTA has landed; the matching wait is at the end of the kernel
+  if (p.bulk_push) {
+    __syncwarp();
+    cluster_arrive_relaxed();
+  }
   if (__all_sync(0xffffffffu, arrived)) {  // warp-uniform: select_rows shuffles
     if (S == 4) select_rows<KMAX, 4>(p, s_partial, s_hist, st, block, krank);
     else if (S == 2) select_rows<KMAX, 2>(p, s_partial, s_hist, st, block, krank);
@@ -308,7 +323,13 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (t < p.stages) mbar_init(full0 + 8 * t, 1);
     else if (t < 2 * p.stages) mbar_init(empty0 + 8 * (t - p.stages), 1);
     else if (t == 2 * p.stages) mbar_init(tmem_full, (uint32_t)p.nacc);  // one commit per issuing warp
-    else mbar_init(part_full, kEpiThreads);  // S source CTAs x (4 / S) warps x 32 lanes
+    else if (!p.bulk_push) mbar_init(part_full, kEpiThreads);  // S source CTAs x (4 / S) warps x 32 lanes
+    else {
+      // bulk exchange: the four quarters this CTA owns arrive as byte counts on the barrier
+      mbar_init(part_full, 1);
+      fence_barrier_init();
+      mbar_expect_tx(part_full, (uint32_t)(4 * 32 * (kChunk + 4) * sizeof(float)));
+    }
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -391,6 +412,7 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
     __syncwarp();
     cluster_wait_acquire();
+    if (p.bulk_push) cluster_arrive_relaxed();  // see the end of the kernel
   } else {
     // ------------------------------ epilogue warps ------------------------------
     asm volatile("bar.sync 2, 192;" ::: "memory");
@@ -447,6 +469,17 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
       for (int i = 0; i < kChunk; i += 4)
         *reinterpret_cast<float4*>(stage + lane * (kChunk + 4) + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
       __syncwarp();
+      if (p.bulk_push) {
+        // (3a) E == 64: the staging tile has the layout of the owner's block (32 rows of E + 4 floats),
+        // so one bulk copy moves the quarter and counts its bytes on the owner's barrier: no remote
+        // store instructions and no release-arrive behind them
+        fence_proxy_async();  // this lane's staging writes, for the async proxy
+        __syncwarp();
+        if (lane == 0)
+          bulk_copy_to_cluster(owner_part, smem_u32(stage), (uint32_t)(32 * (kChunk + 4) * sizeof(float)),
+                               map_to_cta(part_full, (uint32_t)dest));
+        break;
+      }
       // (3) 16 lanes x 16 bytes cover the (up to) 64 columns of one row: two rows per instruction
       const int cl = (lane & 15) * 4;
       if (cl < width) {
@@ -459,7 +492,7 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
     }
-    mbar_arrive_remote(map_to_cta(part_full, (uint32_t)dest));  // releases this thread's stores
+    if (!p.bulk_push) mbar_arrive_remote(map_to_cta(part_full, (uint32_t)dest));  // releases this thread's stores
     select_phase<KMAX>(p, s_partial, s_hist, part_full, (kProducers + ew) * 32 + lane, block, krank);
   }
 
@@ -469,6 +502,11 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
     tc_fence_after();
     tmem_dealloc(*s_tmem, (uint32_t)p.tmem_cols);
   }
+  // A bulk copy reads its source asynchronously and reports only to its destination.  The select
+  // threads of every CTA arrived at the cluster barrier once their own `part_full` had completed (the
+  // MMA warps on their way here), so when it completes every copy of the cluster has landed and no
+  // CTA's shared memory is still being read.
+  if (p.bulk_push) cluster_wait_acquire();
 }
 
 int launch_router(const void* x, const void* w, int tokens, int d, int experts, int top_k, int skew_experts,
@@ -500,6 +538,10 @@ int launch_router(const void* x, const void* w, int tokens, int d, int experts, 
   if (stages < 1) return fail(MOE_ERR_UNSUPPORTED, "router GEMM: shared memory budget exceeded for experts=%d", experts);
   p.stages = stages;
   p.stage_in_ring = stages * stage_bytes >= transpose_bytes;
+  {
+    static const int bulk_on = [] { const char* v = getenv("MOE_B200_ROUTER_BULK"); return (v && v[0] == '0') ? 0 : 1; }();
+    p.bulk_push = (bulk_on && epad == kChunk) ? 1 : 0;
+  }
   if (!p.stage_in_ring) fixed += transpose_bytes;  // few small stages (tiny d_model): the tiles get room of their own
   // every issuing warp needs a stage of its own; both accumulators must fit the 512 TMEM columns
   p.nacc = kMmaWarps;
