@@ -21,10 +21,13 @@
 // third; with 128 x 256 tiles the kernel is bound by L2 -> shared-memory traffic, not by the tensor
 // pipe).  Both accumulators then belong to the same unit, so the epilogue overlaps the next unit's
 // main loop only from its second half on.  An expert with an odd number of tiles ends with a
-// single-tile unit.
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// single-tile unit.  (Those experts run on the two-CTA kernel further down unless it is switched
+// off; pair mode is what remains then.)
+// Warp roles (352 threads): warps 0 and 10 = TMA producers, warp 1 = TMEM owner + MMA issuer,
 // warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4)..; the two warps of a lane quarter split
 // the tile's columns).
+// Two kernels serve a call: this one-CTA kernel and grouped_gemm_cta2_kernel; the routed row count,
+// read on the device, decides which of them works (the other returns at once).
 //
 // Scattered output (`c_rows`): instead of row r of a dense C, every output row goes to its own base
 // address, which may lie in another GPU's memory (a peer mapping).  The expert-parallel layer uses
