@@ -53,6 +53,9 @@ ROUTER_BYTES = T * D * 2 + E * D * 2 + 2 * T * K_TOP * 4 + (T // 32) * E * 4  # 
 ROUTER_DRAM_TRAFFIC = 34_150_000
 SCATTER_DRAM_TRAFFIC = 42_900_000
 WORKLOAD = "fused_select T=4096 d_model=4096 E=64 top_k=2 fp16, +2.0 skew on experts 0..7"
+# the same object in both arms; `l2` says how the GPU arm keeps its inputs out of the L2 between steps
+CONFIG = {"workload": WORKLOAD,
+          "l2": "GPU arm: 5 rotating input/output sets, 480 MiB > 126 MB L2, no flush needed; CPU arm: not applicable"}
 METRIC = "routed tokens/s per MoE layer"
 
 
@@ -193,7 +196,7 @@ def main_reference(args):
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": r["ms"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD},
+        "config": dict(CONFIG),
         "notes": "CPU path of the reference: fp32, the fused_select strategy runs as naive_topk (bench_router.py:498-501); "
                  + r["inputs"],
         "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
@@ -503,7 +506,7 @@ def main_ours(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD},
+            "config": dict(CONFIG),
             "setup": {"tokens_per_gpu": T, "d_model": D, "experts": E, "top_k": K_TOP,
                       "l2": f"{n_sets} rotating input/output sets, {n_sets * (T * D * 2 * 3) >> 20} MiB > 126 MB L2",
                       "launch": "K steps captured in one CUDA graph, replayed `repeats` times"},

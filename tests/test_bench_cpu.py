@@ -24,7 +24,7 @@ def test_reference_arm_prints_the_contract_line():
     sys.path.insert(0, ROOT)
     import bench
 
-    assert line["config"] == {"workload": bench.WORKLOAD}
+    assert line["config"] == bench.CONFIG and line["config"]["workload"] == bench.WORKLOAD
 
 
 def test_reference_runner_falls_back_to_the_port_when_nothing_is_staged(monkeypatch):
