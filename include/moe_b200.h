@@ -22,7 +22,9 @@
  *     in it), MOE_B200_PAIR=0 (single-tile work units), MOE_B200_M64=0
  *     (128-row tiles only), MOE_B200_GEMM_PRODUCERS=1 (one TMA-issuing
  *     warp); MOE_B200_ROUTER_BULK=0 (router kernel: split-K partials exchanged
- *     with remote stores also where a bulk copy would do);
+ *     with remote stores also where a bulk copy would do),
+ *     MOE_B200_ROUTER_PREFETCH=0 (no L2 prefetch of the tokens ahead of the
+ *     dependency wait);
  *     MOE_B200_SINKHORN_CLUSTER=8 (portable cluster size).
  *
  * Each declaration names the piece of the reference (path:lines inside

@@ -58,6 +58,7 @@ struct RouterParams {
   int kblocks, splitk, stages, tmem_cols, num_tiles;
   int stage_in_ring;  // the exchange's transpose tiles reuse the pipeline stages
   int bulk_push;      // the exchange moves a warp's 32 x (E + 4) quarter with one bulk copy (E == 64 only)
+  int prefetch_x;     // request this CTA's token boxes into L2 before the dependency wait
   int nacc;  // MMA-issuing warps = TMEM accumulators (1 or 2; at most the stage count)
   // bit (2 * k-slice rank + m): issuing warp m gets at least one k-block of that k slice, i.e.
   // accumulator m holds a partial sum (the other was never written)
@@ -317,6 +318,13 @@ router_gemm_select_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (threadIdx.x == kThreads - 32) {
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_w);
+    // The tokens are an input of the whole route: nothing this library launches writes them.  Their
+    // boxes are requested into L2 here, ahead of the dependency wait below, so that with programmatic
+    // dependent launch the HBM reads of this route start under the tail of the kernel before it
+    // (in a sequence of routes: under the previous scatter's stores).  Only a hint: the copies into
+    // shared memory are issued after the wait and read whatever L2 then holds.
+    if (p.prefetch_x)
+      for (int it = 0; it < nkb; ++it) tma_prefetch_l2_2d(&tmap_x, (kb0 + it) * kBlockK, block * kBlockTokens);
   }
   if ((int)threadIdx.x < 2 * p.stages + 2) {
     const int t = (int)threadIdx.x;
@@ -541,6 +549,8 @@ int launch_router(const void* x, const void* w, int tokens, int d, int experts, 
   {
     static const int bulk_on = [] { const char* v = getenv("MOE_B200_ROUTER_BULK"); return (v && v[0] == '0') ? 0 : 1; }();
     p.bulk_push = (bulk_on && epad == kChunk) ? 1 : 0;
+    static const int pf_on = [] { const char* v = getenv("MOE_B200_ROUTER_PREFETCH"); return (v && v[0] == '0') ? 0 : 1; }();
+    p.prefetch_x = pf_on;
   }
   if (!p.stage_in_ring) fixed += transpose_bytes;  // few small stages (tiny d_model): the tiles get room of their own
   // every issuing warp needs a stage of its own; both accumulators must fit the 512 TMEM columns
